@@ -1,0 +1,72 @@
+"""ctypes declarations of the C ABI in include/liger_b200.h (one-to-one, no logic)."""
+import ctypes as C
+import os
+
+from .build import LIB_PATH
+
+LIGER_OK = 0
+EPI_STORE, EPI_GELU, EPI_GEGLU, EPI_QKV_SPLIT, EPI_RESIDUAL = 0, 1, 2, 3, 4
+DEV_TIMEOUT, DEV_BOUNDS = 1, 2
+
+
+class LigerError(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__(f"liger error {code}: {msg}")
+        self.code = code
+
+
+class GemmArgs(C.Structure):
+    _fields_ = [
+        ("a", C.c_void_p), ("wt", C.c_void_p), ("c", C.c_void_p), ("bias", C.c_void_p),
+        ("residual", C.c_void_p), ("q_out", C.c_void_p), ("k_out", C.c_void_p), ("v_out", C.c_void_p),
+        ("m", C.c_int), ("n", C.c_int), ("k", C.c_int),
+        ("lda", C.c_int), ("ldw", C.c_int), ("ldc", C.c_int), ("ldr", C.c_int),
+        ("n_begin", C.c_int), ("n_end", C.c_int), ("epilogue", C.c_int),
+        ("seq_len", C.c_int), ("heads", C.c_int), ("head_dim", C.c_int),
+    ]
+
+
+_P, _I, _F, _U32, _SZ = C.c_void_p, C.c_int, C.c_float, C.c_uint32, C.c_size_t
+
+# name -> (restype, argtypes); must list every function declared in include/liger_b200.h
+SIGNATURES = {
+    "liger_last_error": (C.c_char_p, []),
+    "liger_version": (C.c_char_p, []),
+    "liger_device_status": (_I, [C.POINTER(C.c_uint * 4)]),
+    "liger_device_status_clear": (_I, []),
+    "liger_fill_normal": (_I, [_P, _I, _I, _I, _I, _I, _I, _U32, _U32, _F, _F, _I, _P]),
+    "liger_gemm_fp16": (_I, [C.POINTER(GemmArgs), _P]),
+    "liger_transpose_weight": (_I, [_P, _P, _I, _I, _I, _P]),
+    "liger_attention_prefill": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P]),
+    "liger_attention_decode_scratch_bytes": (_SZ, [_I, _I, _I, _I]),
+    "liger_attention_decode": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P]),
+    "liger_layernorm": (_I, [_P, _P, _P, _P, _I, _I, _P]),
+    "liger_add_bias_input_layernorm": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _P]),
+    "liger_add_bias_gelu": (_I, [_P, _P, _I, _I, _P]),
+    "liger_add_qkv_bias_transpose": (_I, [_P] * 9 + [_I] * 4 + [_P]),
+    "liger_transpose_heads": (_I, [_P, _P, _I, _I, _I, _I, _P]),
+}
+
+_lib = None
+
+
+def lib():
+    """The loaded CUDA library.  Raises (never falls back) when it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise LigerError(-2, f"{LIB_PATH} is missing: build it with build_all() (nvcc, sm_100a); there is no CPU path")
+        handle = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def check(rc):
+    """Raise LigerError for a negative return code."""
+    if rc < 0:
+        raise LigerError(rc, lib().liger_last_error().decode())
+    return rc

@@ -1,0 +1,386 @@
+// Attention for sm_100a.
+//
+// Prefill: one kernel replaces the reference's QK^T batched GEMM, masked softmax, P*V batched GEMM
+// and head-merge transpose (src/layer/bert_layer.h:145-168; src/cuda/attention_kernels.cu:543-573,
+// 693-710).  Each CTA owns 64 query rows of one (batch, head); K/V stream through shared memory
+// in 64-key blocks; scores stay in registers and the softmax is an online, warp-level one
+// (running row max / row sum kept per quad of lanes), in fp32.
+//
+// Decode: one query token per sequence against a KV cache, split over the KV length so that the
+// cache streams at HBM rate; a second kernel merges the split partials.
+#include "runtime.h"
+
+namespace liger {
+
+// ---- mma.sync / ldmatrix helpers -----------------------------------------------------------------
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+constexpr int kBr = 64;  // query rows per CTA
+constexpr int kBc = 64;  // keys per block
+constexpr int kAttnThreads = 128;
+
+// element offset of (row, col) in a [rows][D] fp16 tile whose 16-byte chunks are XOR-swizzled by row
+template <int D>
+__device__ __forceinline__ int swz(int row, int col) {
+  return row * D + ((((col >> 3) ^ (row & 7)) << 3) | (col & 7));
+}
+
+// copy a [64][D] tile (rows r0.. of a [nrows][D] matrix, zero-filled past nrows) into shared memory
+template <int D>
+__device__ __forceinline__ void load_tile(__half* s, const __half* __restrict__ g, int r0, int nrows) {
+  constexpr int CPR = D / 8;
+  for (int i = threadIdx.x; i < 64 * CPR; i += kAttnThreads) {
+    const int r = i / CPR, c = i % CPR;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r0 + r < nrows) v = __ldg(reinterpret_cast<const uint4*>(g + (size_t)(r0 + r) * D + c * 8));
+    *reinterpret_cast<uint4*>(s + swz<D>(r, c * 8)) = v;
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(kAttnThreads)
+attention_prefill_kernel(const __half* __restrict__ q, const __half* __restrict__ k, const __half* __restrict__ v,
+                         const __half* __restrict__ mask, __half* __restrict__ out, int S, int heads, int ldo,
+                         float scale, int causal) {
+  extern __shared__ __align__(16) uint8_t smem_attn[];
+  __half* sQ = reinterpret_cast<__half*>(smem_attn);
+  __half* sK = sQ + kBr * D;
+  __half* sV = sK + kBc * D;
+
+  const int q0 = blockIdx.x * kBr;
+  const int head = blockIdx.y;
+  const int b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const size_t bh = ((size_t)b * heads + head) * (size_t)S * D;
+  const __half* qg = q + bh;
+  const __half* kg = k + bh;
+  const __half* vg = v + bh;
+
+  load_tile<D>(sQ, qg, q0, S);
+  __syncthreads();
+
+  // Q fragments for this warp's 16 rows
+  uint32_t qf[D / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    const int row = warp * 16 + (lane & 15);
+    const int col = kk * 16 + (lane >> 4) * 8;
+    ldmatrix_x4(qf[kk], smem_u32(sQ + swz<D>(row, col)));
+  }
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int j = 0; j < D / 8; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f; }
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.0f, 0.0f};
+
+  int nblocks = (S + kBc - 1) / kBc;
+  if (causal && mask == nullptr) {
+    const int last = (q0 + kBr - 1) / kBc + 1;  // blocks past the diagonal contribute exp(-10000 - max) == 0
+    if (last < nblocks) nblocks = last;
+  }
+
+  for (int jb = 0; jb < nblocks; ++jb) {
+    __syncthreads();  // previous block's K/V fully consumed
+    load_tile<D>(sK, kg, jb * kBc, S);
+    load_tile<D>(sV, vg, jb * kBc, S);
+    __syncthreads();
+
+    float s[kBc / 8][4];
+#pragma unroll
+    for (int j = 0; j < kBc / 8; ++j) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f; }
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+      for (int jp = 0; jp < kBc / 16; ++jp) {
+        uint32_t kf[4];
+        const int row = jp * 16 + (lane & 7) + (lane >> 4) * 8;
+        const int col = kk * 16 + ((lane >> 3) & 1) * 8;
+        ldmatrix_x4(kf, smem_u32(sK + swz<D>(row, col)));
+        mma_16816(s[2 * jp], qf[kk], kf[0], kf[1]);
+        mma_16816(s[2 * jp + 1], qf[kk], kf[2], kf[3]);
+      }
+    }
+
+    // scale, mask, running max
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < kBc / 8; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int r = e >> 1;
+        const int qi = q0 + warp * 16 + g + r * 8;
+        const int kj = jb * kBc + j * 8 + 2 * t + (e & 1);
+        float x = s[j][e] * scale;
+        if (kj >= S) {
+          x = -INFINITY;
+        } else if (mask != nullptr) {
+          if (qi < S) x += (1.0f - __half2float(__ldg(mask + ((size_t)b * S + qi) * S + kj))) * -10000.0f;
+        } else if (causal && kj > qi) {
+          x += -10000.0f;
+        }
+        s[j][e] = x;
+        mx[r] = fmaxf(mx[r], x);
+      }
+    }
+    float alpha[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+      mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+      const float m_new = fmaxf(m_run[r], mx[r]);
+      alpha[r] = __expf(m_run[r] - m_new);
+      m_run[r] = m_new;
+      l_run[r] *= alpha[r];
+    }
+#pragma unroll
+    for (int j = 0; j < kBc / 8; ++j) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int r = e >> 1;
+        const float p = __expf(s[j][e] - m_run[r]);
+        s[j][e] = p;
+        l_run[r] += p;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < D / 8; ++j) {
+      o[j][0] *= alpha[0]; o[j][1] *= alpha[0];
+      o[j][2] *= alpha[1]; o[j][3] *= alpha[1];
+    }
+
+    // O += P * V
+#pragma unroll
+    for (int kk = 0; kk < kBc / 16; ++kk) {
+      uint32_t pf[4];
+      pf[0] = pack_half2(s[2 * kk][0], s[2 * kk][1]);
+      pf[1] = pack_half2(s[2 * kk][2], s[2 * kk][3]);
+      pf[2] = pack_half2(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+      pf[3] = pack_half2(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+      for (int dp = 0; dp < D / 16; ++dp) {
+        uint32_t vf[4];
+        const int row = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int col = dp * 16 + (lane >> 4) * 8;
+        ldmatrix_x4_trans(vf, smem_u32(sV + swz<D>(row, col)));
+        mma_16816(o[2 * dp], pf, vf[0], vf[1]);
+        mma_16816(o[2 * dp + 1], pf, vf[2], vf[3]);
+      }
+    }
+  }
+
+  // normalise: p = exp(t - max) / (sum + 1e-6)   (src/cuda/attention_kernels.cu:567-568)
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    float l = l_run[r];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    const float inv = 1.0f / (l + 1e-6f);
+    const int qi = q0 + warp * 16 + g + r * 8;
+    if (qi < S) {
+      __half* dst = out + ((size_t)b * S + qi) * ldo + head * D;
+#pragma unroll
+      for (int j = 0; j < D / 8; ++j) {
+        *reinterpret_cast<uint32_t*>(dst + j * 8 + 2 * t) = pack_half2(o[j][2 * r] * inv, o[j][2 * r + 1] * inv);
+      }
+    }
+  }
+}
+
+// ---- decode ---------------------------------------------------------------------------------------
+constexpr int kDecThreads = 128;
+constexpr int kDecChunk = 256;  // keys per CTA
+
+__host__ __device__ inline int decode_splits(int kv_len) { return (kv_len + kDecChunk - 1) / kDecChunk; }
+
+// partial layout per (b, head, split): [m, l, acc[D]] floats
+template <int D>
+__global__ void __launch_bounds__(kDecThreads)
+attention_decode_partial_kernel(const __half* __restrict__ q, const __half* __restrict__ kc, const __half* __restrict__ vc,
+                                float* __restrict__ scratch, int heads, int kv_len, int kv_stride, float scale) {
+  constexpr int LPK = D / 8;        // lanes per key (16 B each)
+  constexpr int KPW = 32 / LPK;     // keys per warp per step
+  __shared__ float s_m[kDecThreads / 32][KPW];
+  __shared__ float s_l[kDecThreads / 32][KPW];
+  __shared__ float s_acc[kDecThreads / 32][KPW][D];
+
+  const int split = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
+  const int nsplit = gridDim.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane / LPK, li = lane % LPK;
+  const size_t bh = (size_t)b * heads + head;
+  const __half* kbase = kc + bh * (size_t)kv_stride * D;
+  const __half* vbase = vc + bh * (size_t)kv_stride * D;
+
+  float qv[8];
+  {
+    uint4 u = __ldg(reinterpret_cast<const uint4*>(q + bh * D + li * 8));
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = __half22float2(h[j]);
+      qv[2 * j] = f.x * scale;
+      qv[2 * j + 1] = f.y * scale;
+    }
+  }
+  float m = -INFINITY, l = 0.0f, acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  const int k_begin = split * kDecChunk;
+  const int k_end = min(kv_len, k_begin + kDecChunk);
+  // every lane of a warp runs the same number of steps (the shuffles need the full warp); a
+  // sub-group whose key falls past the end of the chunk just skips the update
+  for (int base = k_begin + warp * KPW; base < k_end; base += (kDecThreads / 32) * KPW) {
+    const int key = base + sub;
+    const bool valid = key < k_end;
+    uint4 ku = make_uint4(0, 0, 0, 0), vu = make_uint4(0, 0, 0, 0);
+    if (valid) {
+      ku = __ldg(reinterpret_cast<const uint4*>(kbase + (size_t)key * D + li * 8));
+      vu = __ldg(reinterpret_cast<const uint4*>(vbase + (size_t)key * D + li * 8));
+    }
+    const __half2* kh = reinterpret_cast<const __half2*>(&ku);
+    float dot = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 f = __half22float2(kh[j]);
+      dot += qv[2 * j] * f.x + qv[2 * j + 1] * f.y;
+    }
+#pragma unroll
+    for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    if (valid) {
+      const float m_new = fmaxf(m, dot);
+      const float alpha = __expf(m - m_new);
+      const float p = __expf(dot - m_new);
+      l = l * alpha + p;
+      const __half2* vh = reinterpret_cast<const __half2*>(&vu);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __half22float2(vh[j]);
+        acc[2 * j] = acc[2 * j] * alpha + p * f.x;
+        acc[2 * j + 1] = acc[2 * j + 1] * alpha + p * f.y;
+      }
+      m = m_new;
+    }
+  }
+  if (li == 0) { s_m[warp][sub] = m; s_l[warp][sub] = l; }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s_acc[warp][sub][li * 8 + j] = acc[j];
+  __syncthreads();
+  // merge the (warps x KPW) partial states; thread d < D owns one output column
+  if (threadIdx.x < D) {
+    float mm = -INFINITY;
+    for (int w = 0; w < kDecThreads / 32; ++w)
+      for (int s2 = 0; s2 < KPW; ++s2) mm = fmaxf(mm, s_m[w][s2]);
+    float ll = 0.0f, a = 0.0f;
+    for (int w = 0; w < kDecThreads / 32; ++w)
+      for (int s2 = 0; s2 < KPW; ++s2) {
+        const float mw = s_m[w][s2];
+        const float sc = (mw == -INFINITY) ? 0.0f : __expf(mw - mm);
+        ll += s_l[w][s2] * sc;
+        a += s_acc[w][s2][threadIdx.x] * sc;
+      }
+    float* dst = scratch + (bh * nsplit + split) * (size_t)(D + 2);
+    if (threadIdx.x == 0) { dst[0] = mm; dst[1] = ll; }
+    dst[2 + threadIdx.x] = a;
+  }
+}
+
+template <int D>
+__global__ void attention_decode_merge_kernel(const float* __restrict__ scratch, __half* __restrict__ out, int heads,
+                                              int nsplit, int ldo) {
+  const int head = blockIdx.x, b = blockIdx.y;
+  const size_t bh = (size_t)b * heads + head;
+  const float* src = scratch + bh * nsplit * (size_t)(D + 2);
+  const int d = threadIdx.x;
+  float mm = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) mm = fmaxf(mm, src[(size_t)s * (D + 2)]);
+  float ll = 0.0f, a = 0.0f;
+  for (int s = 0; s < nsplit; ++s) {
+    const float ms = src[(size_t)s * (D + 2)];
+    const float sc = (ms == -INFINITY) ? 0.0f : __expf(ms - mm);
+    ll += src[(size_t)s * (D + 2) + 1] * sc;
+    a += src[(size_t)s * (D + 2) + 2 + d] * sc;
+  }
+  out[(size_t)b * ldo + head * D + d] = __float2half_rn(a / (ll + 1e-6f));
+}
+
+template <int D>
+static int launch_prefill(const void* q, const void* k, const void* v, const void* mask, void* out, int batch, int heads,
+                          int S, int ldo, float scale, int causal, cudaStream_t stream) {
+  const int smem = (kBr + 2 * kBc) * D * 2;
+  LIGER_CUDA_TRY(cudaFuncSetAttribute(attention_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  dim3 grid((S + kBr - 1) / kBr, heads, batch);
+  attention_prefill_kernel<D><<<grid, kAttnThreads, smem, stream>>>((const __half*)q, (const __half*)k, (const __half*)v,
+                                                                   (const __half*)mask, (__half*)out, S, heads, ldo,
+                                                                   scale, causal);
+  return check_launch("attention_prefill_kernel");
+}
+
+}  // namespace liger
+
+using namespace liger;
+
+extern "C" int liger_attention_prefill(const void* q, const void* k, const void* v, const void* mask, void* out, int batch,
+                                       int heads, int seq_len, int head_dim, int ldo, float scale, int causal,
+                                       void* stream) {
+  if (!q || !k || !v || !out || batch <= 0 || heads <= 0 || seq_len <= 0)
+    return set_error(LIGER_ERR_INVALID, "attention_prefill: bad argument");
+  if (ldo < heads * head_dim || ldo % 2) return set_error(LIGER_ERR_INVALID, "attention_prefill: ldo must be even and >= heads*head_dim");
+  if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v) & 15u || ((uintptr_t)out & 3u))
+    return set_error(LIGER_ERR_INVALID, "attention_prefill: q/k/v must be 16-byte aligned");
+  if (batch > 65535 || heads > 65535) return set_error(LIGER_ERR_UNSUPPORTED, "attention_prefill: batch, heads <= 65535");
+  if (!current_device()) return LIGER_ERR_CUDA;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (head_dim == 64) return launch_prefill<64>(q, k, v, mask, out, batch, heads, seq_len, ldo, scale, causal, s);
+  if (head_dim == 128) return launch_prefill<128>(q, k, v, mask, out, batch, heads, seq_len, ldo, scale, causal, s);
+  return set_error(LIGER_ERR_UNSUPPORTED, "attention_prefill: head_dim %d (64 and 128 are implemented)", head_dim);
+}
+
+extern "C" size_t liger_attention_decode_scratch_bytes(int batch, int heads, int head_dim, int kv_len) {
+  if (batch <= 0 || heads <= 0 || head_dim <= 0 || kv_len <= 0) return 0;
+  return (size_t)batch * heads * decode_splits(kv_len) * (size_t)(head_dim + 2) * sizeof(float);
+}
+
+extern "C" int liger_attention_decode(const void* q, const void* k_cache, const void* v_cache, void* out, void* scratch,
+                                      int batch, int heads, int kv_len, int kv_stride, int head_dim, int ldo, float scale,
+                                      void* stream) {
+  if (!q || !k_cache || !v_cache || !out || !scratch || batch <= 0 || heads <= 0 || kv_len <= 0 || kv_stride < kv_len)
+    return set_error(LIGER_ERR_INVALID, "attention_decode: bad argument");
+  if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15u)
+    return set_error(LIGER_ERR_INVALID, "attention_decode: q / caches must be 16-byte aligned");
+  if (batch > 65535 || heads > 65535) return set_error(LIGER_ERR_UNSUPPORTED, "attention_decode: batch, heads <= 65535");
+  if (!current_device()) return LIGER_ERR_CUDA;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int ns = decode_splits(kv_len);
+  dim3 grid(ns, heads, batch), mgrid(heads, batch);
+  if (head_dim == 128) {
+    attention_decode_partial_kernel<128><<<grid, kDecThreads, 0, s>>>((const __half*)q, (const __half*)k_cache,
+                                                                      (const __half*)v_cache, (float*)scratch, heads,
+                                                                      kv_len, kv_stride, scale);
+    int rc = check_launch("attention_decode_partial_kernel");
+    if (rc != LIGER_OK) return rc;
+    attention_decode_merge_kernel<128><<<mgrid, 128, 0, s>>>((const float*)scratch, (__half*)out, heads, ns, ldo);
+  } else if (head_dim == 64) {
+    attention_decode_partial_kernel<64><<<grid, kDecThreads, 0, s>>>((const __half*)q, (const __half*)k_cache,
+                                                                     (const __half*)v_cache, (float*)scratch, heads,
+                                                                     kv_len, kv_stride, scale);
+    int rc = check_launch("attention_decode_partial_kernel");
+    if (rc != LIGER_OK) return rc;
+    attention_decode_merge_kernel<64><<<mgrid, 64, 0, s>>>((const float*)scratch, (__half*)out, heads, ns, ldo);
+  } else {
+    return set_error(LIGER_ERR_UNSUPPORTED, "attention_decode: head_dim %d (64 and 128 are implemented)", head_dim);
+  }
+  return check_launch("attention_decode_merge_kernel");
+}

@@ -1,0 +1,382 @@
+// fp16 GEMM for sm_100a: C[M, n_begin:n_end] = epilogue(A[M,K] * W[K,N]), fp32 accumulation.
+//
+// Replaces the reference's cublasGemmEx calls (GemmEx, src/layer/func_wrapper.h:20-27, bound by
+// Linear_Col / Linear_Row at src/layer/linear.h:47-53,99-105) and, through its epilogues, the
+// element-wise kernels that follow them (add_QKV_bias, add_bias_gelu).
+//
+// Structure (one persistent CTA per SM, 6 warps):
+//   warp 0  : TMA producer  -- one thread streams 128x64 A tiles and BNx64 W^T tiles into a
+//             STAGES-deep shared-memory ring (128-byte swizzle), signalling `full` mbarriers.
+//   warp 1  : MMA issuer    -- one thread issues tcgen05.mma (M=128, N=BN, K=16) x4 per stage into
+//             one of two TMEM accumulators; tcgen05.commit releases the stage (`empty`) and,
+//             after the last k-block, hands the accumulator to the epilogue (`tmem_full`).
+//   warps 2-5: epilogue     -- tcgen05.ld 32 columns at a time (thread = row), bias / activation /
+//             scatter in registers, 16-byte fp16 stores; then `tmem_empty` lets the MMA warp
+//             reuse the accumulator, so the epilogue of tile i overlaps the MMAs of tile i+1.
+// All waits are bounded (common.cuh); a timeout sets the sticky status word and the CTA unwinds.
+#include "runtime.h"
+
+namespace liger {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int kGemmThreads = 192;
+
+struct GemmParams {
+  __half* c;
+  const __half* bias;
+  const __half* residual;
+  __half* qkv[3];
+  int m, n_begin, n_end;
+  int ldc, ldr;
+  int epilogue;
+  int seq_len, heads, head_dim;
+  int tiles_m, tiles_n, kblocks;
+  DeviceStatus* status;
+};
+
+template <int BN, int STAGES>
+struct GemmCfg {
+  static constexpr int kABytes = BM * BK * 2;
+  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kSmemBytes = STAGES * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+  static constexpr int kTmemCols = 2 * BN;
+};
+
+// ---- epilogue helpers -------------------------------------------------------------------------
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __half22float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+
+// 32 accumulator columns [col0, col0+32) of one row -> bias / activation -> fp16 stores.
+__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, int row, int col0, const uint32_t (&r)[32]) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const int col = col0 + g * 8;
+    if (col >= p.n_end) break;
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]);
+    if (p.bias != nullptr) {
+      float b[8];
+      unpack8(__ldg(reinterpret_cast<const uint4*>(p.bias + col)), b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] += b[i];
+    }
+    if (p.epilogue == LIGER_EPI_GELU) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = gelu_tanh(v[i]);
+    } else if (p.epilogue == LIGER_EPI_RESIDUAL) {
+      float b[8];
+      unpack8(__ldg(reinterpret_cast<const uint4*>(p.residual + (size_t)row * p.ldr + col)), b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] += b[i];
+    }
+    uint4 o;
+    o.x = pack_half2(v[0], v[1]);
+    o.y = pack_half2(v[2], v[3]);
+    o.z = pack_half2(v[4], v[5]);
+    o.w = pack_half2(v[6], v[7]);
+    __half* dst;
+    if (p.epilogue == LIGER_EPI_QKV_SPLIT) {
+      const int hd = p.heads * p.head_dim;
+      const int which = col / hd;
+      const int rem = col - which * hd;
+      const int head = rem / p.head_dim;
+      const int d = rem - head * p.head_dim;
+      const int b = row / p.seq_len;
+      const int s = row - b * p.seq_len;
+      dst = p.qkv[which] + (((size_t)b * p.heads + head) * p.seq_len + s) * p.head_dim + d;
+    } else {
+      dst = p.c + (size_t)row * p.ldc + col;
+    }
+    *reinterpret_cast<uint4*>(dst) = o;
+  }
+}
+
+// gate chunk + value chunk -> 32 outputs gelu(gate + b) * (value + b) at column out_col0
+__device__ __forceinline__ void epilogue_geglu(const GemmParams& p, int row, int col0, int out_col0,
+                                               const uint32_t (&g)[32], const uint32_t (&u)[32]) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    float gv[8], uv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      gv[i] = __uint_as_float(g[q * 8 + i]);
+      uv[i] = __uint_as_float(u[q * 8 + i]);
+    }
+    if (p.bias != nullptr) {
+      float b[8];
+      unpack8(__ldg(reinterpret_cast<const uint4*>(p.bias + col0 + q * 8)), b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) gv[i] += b[i];
+      unpack8(__ldg(reinterpret_cast<const uint4*>(p.bias + col0 + 32 + q * 8)), b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) uv[i] += b[i];
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) gv[i] = gelu_tanh(gv[i]) * uv[i];
+    uint4 o;
+    o.x = pack_half2(gv[0], gv[1]);
+    o.y = pack_half2(gv[2], gv[3]);
+    o.z = pack_half2(gv[4], gv[5]);
+    o.w = pack_half2(gv[6], gv[7]);
+    *reinterpret_cast<uint4*>(p.c + (size_t)row * p.ldc + out_col0 + q * 8) = o;
+  }
+}
+
+// ---- the kernel -------------------------------------------------------------------------------
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const GemmParams p) {
+  using Cfg = GemmCfg<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::kStageBytes);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full = empty_bar + STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 4);  // one arrival per epilogue warp
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = p.tiles_m * p.tiles_n;
+
+  if (warp == 0) {
+    // ===== TMA producer =====
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      uint32_t armed_mask = 0, armed_phase = 0;  // which stages have a load in flight, and its parity
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const int m0 = (t % p.tiles_m) * BM;
+        const int n0 = p.n_begin + (t / p.tiles_m) * BN;
+        for (int kb = 0; kb < p.kblocks; ++kb) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+          uint8_t* sa = smem + stage * Cfg::kStageBytes;
+          mbar_arrive_expect_tx(&full_bar[stage], Cfg::kStageBytes);
+          tma_load_2d(sa, &tmap_a, &full_bar[stage], kb * BK, m0);
+          tma_load_2d(sa + Cfg::kABytes, &tmap_b, &full_bar[stage], kb * BK, n0);
+          armed_mask |= 1u << stage;
+          armed_phase = (armed_phase & ~(1u << stage)) | (phase << stage);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // unwinding: give the copies already issued a bounded time to land before the CTA exits
+        for (int s = 0; s < STAGES; ++s)
+          if (armed_mask & (1u << s))
+            for (int spin = 0; spin < (1 << 16) && !mbar_test(&full_bar[s], (armed_phase >> s) & 1u); ++spin) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ===== MMA issuer =====
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(BM, BN);
+      uint32_t stage = 0, phase = 0, it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+        const uint32_t acc = it & 1u, acc_phase = (it >> 1) & 1u;
+        if (!mbar_wait_bounded(&tmem_empty[acc], acc_phase ^ 1u, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.kblocks; ++kb) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint64_t da = make_sw128_kmajor_desc(sa);
+          const uint64_t db = make_sw128_kmajor_desc(sa + Cfg::kABytes);
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 16; ++k4) {
+            // advancing 16 fp16 along K inside the 128-byte swizzle atom = +32 bytes = +2 in the
+            // descriptor's (address >> 4) field
+            umma_f16(d_tmem, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc, (kb | k4) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) umma_commit(&tmem_full[acc]);
+      }
+    }
+  } else {
+    // ===== epilogue: warps 2..5, TMEM lane quadrant = warp % 4 =====
+    const int quad = warp & 3;
+    uint32_t it = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+      const uint32_t acc = it & 1u, acc_phase = (it >> 1) & 1u;
+      const int m0 = (t % p.tiles_m) * BM;
+      const int n0 = p.n_begin + (t / p.tiles_m) * BN;
+      if (!mbar_wait_bounded(&tmem_full[acc], acc_phase, abort_flag)) break;
+      tc_fence_after();
+      const int row = m0 + quad * 32 + lane;
+      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
+      if (p.epilogue == LIGER_EPI_GEGLU) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          const int col0 = n0 + c * 64;
+          if (col0 >= p.n_end) break;
+          uint32_t g[32], u[32];
+          tmem_ld_32x32(taddr + c * 64, g);
+          tmem_ld_32x32(taddr + c * 64 + 32, u);
+          tmem_ld_wait();
+          if (row < p.m) epilogue_geglu(p, row, col0, col0 >> 1, g, u);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col0 = n0 + c * 32;
+          if (col0 >= p.n_end) break;
+          uint32_t r[32];
+          tmem_ld_32x32(taddr + c * 32, r);
+          tmem_ld_wait();
+          if (row < p.m) epilogue_chunk(p, row, col0, r);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+    }
+  }
+
+  // ===== teardown =====
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    __syncwarp();
+    tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag) report_failure(p.status, LIGER_DEV_TIMEOUT, 0x100u, blockIdx.x, 0);
+}
+
+template <int BN, int STAGES>
+static int launch_gemm(const liger_gemm_args& a, const GemmParams& p0, int sm_count, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN, STAGES>;
+  GemmParams p = p0;
+  p.tiles_m = (a.m + BM - 1) / BM;
+  p.tiles_n = (a.n_end - a.n_begin + BN - 1) / BN;
+  p.kblocks = (a.k + BK - 1) / BK;
+  CUtensorMap tm_a, tm_b;
+  int rc;
+  if ((rc = make_tmap_2d_f16(&tm_a, a.a, (uint64_t)a.k, (uint64_t)a.m, (uint64_t)a.lda, BK, BM)) != LIGER_OK) return rc;
+  if ((rc = make_tmap_2d_f16(&tm_b, a.wt, (uint64_t)a.k, (uint64_t)a.n, (uint64_t)a.ldw, BK, BN)) != LIGER_OK) return rc;
+  static bool attr_set = false;  // per template instantiation
+  if (!attr_set) {
+    LIGER_CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        Cfg::kSmemBytes));
+    attr_set = true;
+  }
+  const int tiles = p.tiles_m * p.tiles_n;
+  const int grid = tiles < sm_count ? tiles : sm_count;
+  gemm_tcgen05_kernel<BN, STAGES><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(tm_a, tm_b, p);
+  return check_launch("gemm_tcgen05_kernel");
+}
+
+}  // namespace liger
+
+extern "C" int liger_gemm_fp16(const liger_gemm_args* args, void* stream) {
+  using namespace liger;
+  if (!args) return set_error(LIGER_ERR_INVALID, "liger_gemm_fp16: null args");
+  const liger_gemm_args& a = *args;
+  if (a.m <= 0 || a.n <= 0 || a.k <= 0) return set_error(LIGER_ERR_INVALID, "gemm: m, n, k must be positive");
+  if (!a.a || !a.wt) return set_error(LIGER_ERR_INVALID, "gemm: null operand");
+  if (a.k % 8 || a.lda % 8 || a.ldw % 8 || a.lda < a.k || a.ldw < a.k)
+    return set_error(LIGER_ERR_INVALID, "gemm: k, lda, ldw must be multiples of 8 and lda, ldw >= k");
+  if (a.n_begin < 0 || a.n_end > a.n || a.n_begin >= a.n_end || a.n_begin % 8 || a.n_end % 8)
+    return set_error(LIGER_ERR_INVALID, "gemm: bad feature slice [%d, %d) of %d (bounds must be multiples of 8)",
+                     a.n_begin, a.n_end, a.n);
+  if (a.bias && ((uintptr_t)a.bias & 15u)) return set_error(LIGER_ERR_INVALID, "gemm: bias must be 16-byte aligned");
+  GemmParams p{};
+  p.c = (__half*)a.c;
+  p.bias = (const __half*)a.bias;
+  p.residual = (const __half*)a.residual;
+  p.m = a.m; p.n_begin = a.n_begin; p.n_end = a.n_end;
+  p.ldc = a.ldc; p.ldr = a.ldr;
+  p.epilogue = a.epilogue;
+  switch (a.epilogue) {
+    case LIGER_EPI_STORE:
+    case LIGER_EPI_GELU:
+    case LIGER_EPI_RESIDUAL:
+    case LIGER_EPI_GEGLU:
+      if (!a.c || ((uintptr_t)a.c & 15u) || a.ldc % 8)
+        return set_error(LIGER_ERR_INVALID, "gemm: c must be 16-byte aligned with ldc %% 8 == 0");
+      if (a.epilogue == LIGER_EPI_RESIDUAL && (!a.residual || ((uintptr_t)a.residual & 15u) || a.ldr % 8))
+        return set_error(LIGER_ERR_INVALID, "gemm: residual must be 16-byte aligned with ldr %% 8 == 0");
+      if (a.epilogue == LIGER_EPI_GEGLU && (a.n % 64 || a.n_begin % 64 || a.n_end % 64))
+        return set_error(LIGER_ERR_INVALID, "gemm: GeGLU needs n, n_begin, n_end to be multiples of 64");
+      break;
+    case LIGER_EPI_QKV_SPLIT:
+      if (!a.q_out || !a.k_out || !a.v_out || a.seq_len <= 0 || a.heads <= 0 || a.head_dim <= 0)
+        return set_error(LIGER_ERR_INVALID, "gemm: QKV split needs q/k/v outputs and seq_len, heads, head_dim");
+      if (a.n != 3 * a.heads * a.head_dim || a.head_dim % 8 || a.m % a.seq_len)
+        return set_error(LIGER_ERR_INVALID, "gemm: QKV split needs n == 3*heads*head_dim, head_dim %% 8 == 0, m %% seq_len == 0");
+      if (((uintptr_t)a.q_out | (uintptr_t)a.k_out | (uintptr_t)a.v_out) & 15u)
+        return set_error(LIGER_ERR_INVALID, "gemm: q/k/v outputs must be 16-byte aligned");
+      p.qkv[0] = (__half*)a.q_out; p.qkv[1] = (__half*)a.k_out; p.qkv[2] = (__half*)a.v_out;
+      p.seq_len = a.seq_len; p.heads = a.heads; p.head_dim = a.head_dim;
+      break;
+    default:
+      return set_error(LIGER_ERR_INVALID, "gemm: unknown epilogue %d", a.epilogue);
+  }
+  const DeviceInfo* dev;
+  int rc = require_sm100(&dev);
+  if (rc != LIGER_OK) return rc;
+  p.status = dev->status_dev;
+
+  // Tile-width choice: fewest (waves x per-tile cost); per-tile cost ~ (BM + BN) (operand bytes per
+  // k-block and MMA time are both linear in BN).  GeGLU pairs 32-column chunks, so BN >= 64 there.
+  const int tiles_m = (a.m + BM - 1) / BM;
+  const int span = a.n_end - a.n_begin;
+  int best_bn = 256;
+  long best_cost = -1;
+  const int cands[4] = {256, 128, 64, 32};
+  for (int i = 0; i < 4; ++i) {
+    const int bn = cands[i];
+    if (a.epilogue == LIGER_EPI_GEGLU && bn < 64) continue;
+    const long tiles = (long)tiles_m * ((span + bn - 1) / bn);
+    const long waves = (tiles + dev->sm_count - 1) / dev->sm_count;
+    const long cost = waves * (BM + bn);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_bn = bn; }
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (best_bn) {
+    case 256: return launch_gemm<256, 4>(a, p, dev->sm_count, s);
+    case 128: return launch_gemm<128, 6>(a, p, dev->sm_count, s);
+    case 64: return launch_gemm<64, 8>(a, p, dev->sm_count, s);
+    default: return launch_gemm<32, 8>(a, p, dev->sm_count, s);
+  }
+}

@@ -1,0 +1,194 @@
+/*
+ * liger_b200.h -- C ABI of the B200 (sm_100a) implementation of Liger's tensor-parallel
+ * transformer-layer path.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, launches asynchronously on
+ * the CUDA stream it is given (passed as void*, i.e. a cudaStream_t) and returns LIGER_OK or a
+ * negative LIGER_ERR_* code; liger_last_error() gives the message for the calling thread.  All
+ * tensors are fp16 (IEEE binary16) in device memory and row-major unless stated otherwise; all
+ * accumulation is fp32.  There is no CPU fallback: without a CUDA device every compute entry
+ * point fails with LIGER_ERR_CUDA.
+ *
+ * Citations of the form `src/...:lines` name the interface of the reference implementation
+ * (MachineLearningSystem/24PPOPP-Liger) that the entry point replaces.
+ */
+#ifndef LIGER_B200_H
+#define LIGER_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define LIGER_API __attribute__((visibility("default")))
+#else
+#define LIGER_API
+#endif
+
+#define LIGER_OK 0
+#define LIGER_ERR_INVALID (-1)     /* bad argument (shape, alignment, null pointer) */
+#define LIGER_ERR_CUDA (-2)        /* a CUDA runtime / driver call failed */
+#define LIGER_ERR_UNSUPPORTED (-3) /* shape outside what the kernels implement */
+#define LIGER_ERR_DEVICE (-4)      /* the sticky device status word is set (timeout, bounds) */
+#define LIGER_ERR_TOO_LARGE (-5)   /* a fixed-capacity resource is too small for the request */
+#define LIGER_ERR_COMM (-6)        /* communicator set-up failed */
+
+/* bits of the sticky device status word */
+#define LIGER_DEV_TIMEOUT 1u /* a bounded device-side wait ran out */
+#define LIGER_DEV_BOUNDS 2u  /* an index check inside a kernel failed; the access was skipped */
+
+/* Message describing the last error returned to the calling thread ("" if none). */
+LIGER_API const char* liger_last_error(void);
+
+/* Library version string. */
+LIGER_API const char* liger_version(void);
+
+/*
+ * Sticky device status.  Kernels never trap or spin forever: a wait that exceeds its budget or
+ * an index that fails a check sets a bit in a host-visible status word and the kernel unwinds.
+ * out[0] = LIGER_DEV_* bits, out[1] = location id, out[2..3] = detail.  Returns out[0].
+ * The reference ignores every CUDA / cuBLAS / NCCL return code (e.g. src/layer/func_wrapper.h:25,42).
+ */
+LIGER_API int liger_device_status(unsigned int out[4]);
+LIGER_API int liger_device_status_clear(void);
+
+/* ------------------------------------------------------------------------------------------ */
+/* Seeded tensors (the reference leaves every buffer uninitialised: src/layer/linear.h:40,92,  */
+/* src/layer/bert_layer.h:45,115-118, src/layer/operator.h:29-30, src/test_schedule.h:29-31)  */
+/* ------------------------------------------------------------------------------------------ */
+
+/*
+ * dst[r*dst_ld + c] (r < rows, c < cols) = element (row0 + r, col0 + c) of the seeded logical
+ * matrix `tensor_id` with `src_ld` columns: fp16(mean + std * N(0,1)), a pure function of
+ * (seed, tensor_id, element index).  transpose = 1 writes the window transposed, dst[c*dst_ld + r];
+ * transpose = 2 / 3 also transposes but sends logical column c to row (c/32)*64 + c%32 (+32 for 3),
+ * the gate / value rows of the interleaved LIGER_EPI_GEGLU weight layout (cols % 32 == 0).
+ */
+LIGER_API int liger_fill_normal(void* dst, int rows, int cols, int dst_ld, int row0, int col0, int src_ld, uint32_t seed,
+                      uint32_t tensor_id, float mean, float std, int transpose, void* stream);
+
+/* ------------------------------------------------------------------------------------------ */
+/* Dense contractions                                                                         */
+/* ------------------------------------------------------------------------------------------ */
+
+enum liger_epilogue {
+  LIGER_EPI_STORE = 0,     /* C = acc (+ bias)                                                  */
+  LIGER_EPI_GELU = 1,      /* C = gelu_tanh(acc + bias)                                         */
+  LIGER_EPI_GEGLU = 2,     /* C[:, j] = gelu_tanh(gate_j + b) * (value_j + b); C has N/2 columns */
+  LIGER_EPI_QKV_SPLIT = 3, /* acc + bias scattered to q / k / v in [B, h, S, D] layout          */
+  LIGER_EPI_RESIDUAL = 4   /* C = acc + bias + residual                                         */
+};
+
+/*
+ * C[M, n_begin:n_end] = epilogue(A[M,K] * W[K,N]) on the tcgen05 tensor cores.
+ *
+ * Replaces GemmEx (src/layer/func_wrapper.h:20-27) as bound by Linear_Col / Linear_Row
+ * (src/layer/linear.h:47-53, 99-105).  LIGER_EPI_QKV_SPLIT also replaces Add_QKV_bias_transpose
+ * (src/layer/func_wrapper.h:57-62), LIGER_EPI_GELU replaces Add_bias_act_kernelLauncher
+ * (src/layer/func_wrapper.h:90-94).
+ *
+ * The weight is passed pre-transposed: wt[n*ldw + k] = W[k][n] (K contiguous), which is how this
+ * library stores weights (liger_fill_normal(..., transpose=1) or liger_transpose_weight produce
+ * it from the reference orientation).  n_begin / n_end select a slice of output features: the
+ * reference's kernel decomposition (decompose_callback, src/utils.h:218-260) maps to launches
+ * with consecutive slices, and -- unlike the reference, whose slices restart at column 0 -- the
+ * slices tile N exactly, so the union of the slices equals one whole launch bit for bit.
+ *
+ * Requirements: K % 8 == 0, lda % 8 == 0, ldw % 8 == 0, a / wt 16-byte aligned, ldc % 8 == 0 and
+ * c 16-byte aligned, n_begin % 8 == 0.
+ * For LIGER_EPI_GEGLU the rows of wt must be interleaved in blocks of 32 (32 gate rows, then the
+ * 32 matching value rows); n_begin / n_end are in that interleaved space, multiples of 64, and
+ * the result occupies columns [n_begin/2, n_end/2) of c.
+ * For LIGER_EPI_QKV_SPLIT, N = 3 * heads * head_dim, row m = b * seq_len + s, and feature
+ * n = which * heads * head_dim + head * head_dim + d is stored to
+ * {q,k,v}_out[which][((b * heads + head) * seq_len + s) * head_dim + d].
+ */
+typedef struct liger_gemm_args {
+  const void* a;        /* [M, K] fp16 */
+  const void* wt;       /* [N, K] fp16 */
+  void* c;              /* [M, ldc] fp16 (unused for QKV_SPLIT) */
+  const void* bias;     /* [N] fp16 or NULL */
+  const void* residual; /* [M, ldr] fp16, LIGER_EPI_RESIDUAL only */
+  void* q_out;          /* LIGER_EPI_QKV_SPLIT only */
+  void* k_out;
+  void* v_out;
+  int m, n, k;
+  int lda, ldw, ldc, ldr;
+  int n_begin, n_end;
+  int epilogue;
+  int seq_len, heads, head_dim; /* LIGER_EPI_QKV_SPLIT only */
+} liger_gemm_args;
+
+LIGER_API int liger_gemm_fp16(const liger_gemm_args* args, void* stream);
+
+/* dst[n*K + k] = src[k*N + n]: imports a weight from the reference orientation W[k][n]
+ * (src/layer/linear.h:40,92) into the K-contiguous layout liger_gemm_fp16 reads.  With
+ * interleave32 != 0, N must be a multiple of 64 and output row block order becomes
+ * (32 rows of the first half, 32 rows of the second half, ...), the LIGER_EPI_GEGLU layout. */
+LIGER_API int liger_transpose_weight(const void* src, void* dst, int k, int n, int interleave32, void* stream);
+
+/* ------------------------------------------------------------------------------------------ */
+/* Attention                                                                                  */
+/* ------------------------------------------------------------------------------------------ */
+
+/*
+ * out[b*S + s, head*D + d] = sum_k softmax_k(scale * q.k + (1 - mask) * -10000) v  -- one kernel for
+ * the reference's QK^T batched GEMM, masked softmax, P*V batched GEMM and head-merge transpose
+ * (src/layer/bert_layer.h:145-168; Attn_softmax_kernel and Transpose_kernel,
+ * src/layer/func_wrapper.h:71-81).  q, k, v are [B, h, S, D] (the layout LIGER_EPI_QKV_SPLIT
+ * writes); out is [B*S, ldo] with ldo >= h*D.  mask is [B, S, S] fp16 of 0/1 shared over heads
+ * (src/cuda/attention_kernels.cu:544), or NULL with causal = 1 for a causal mask or causal = 0
+ * for none.  Scores never leave the chip; the softmax is computed in fp32 (the reference's half
+ * path scales, masks and exponentiates in fp16: src/cuda/attention_kernels.cu:561-567).
+ * D must be 64 or 128; S is unrestricted (the reference stops at 2048).
+ */
+LIGER_API int liger_attention_prefill(const void* q, const void* k, const void* v, const void* mask, void* out, int batch,
+                            int heads, int seq_len, int head_dim, int ldo, float scale, int causal, void* stream);
+
+/*
+ * Decode step: one new query token per sequence against a KV cache.  q is [B, h, D];
+ * k_cache / v_cache are [B, h, L_max, D] holding kv_len valid positions; out is [B, ldo].
+ * The KV range is split across CTAs; partial results live in `scratch` (float,
+ * liger_attention_decode_scratch_bytes() bytes).  No reference counterpart: the reference has no
+ * KV cache or decode path.
+ */
+LIGER_API size_t liger_attention_decode_scratch_bytes(int batch, int heads, int head_dim, int kv_len);
+LIGER_API int liger_attention_decode(const void* q, const void* k_cache, const void* v_cache, void* out, void* scratch,
+                           int batch, int heads, int kv_len, int kv_stride, int head_dim, int ldo, float scale,
+                           void* stream);
+
+/* ------------------------------------------------------------------------------------------ */
+/* Row-wise operators                                                                         */
+/* ------------------------------------------------------------------------------------------ */
+
+/* y = LayerNorm(x) over the last dimension, eps 1e-6, biased variance, fp32 statistics.
+ * Replaces Layer_Norm (src/layer/func_wrapper.h:110-114 -> src/cuda/cuda_kernels.cu:463-532). */
+LIGER_API int liger_layernorm(const void* x, const void* gamma, const void* beta, void* y, int m, int n, void* stream);
+
+/* out = in + out + bias (stored in place), norm = LayerNorm(out) when norm != NULL.
+ * Replaces Add_bias_input_layernorm_2_kernelLauncher and Add_bias_input_kernelLauncher
+ * (src/layer/func_wrapper.h:96-108 -> src/cuda/cuda_kernels.cu:360-461). bias may be NULL. */
+LIGER_API int liger_add_bias_input_layernorm(const void* in, const void* gamma, const void* beta, const void* bias, void* out,
+                                   void* norm, int m, int n, void* stream);
+
+/* x = gelu_tanh(x + bias) in place. Replaces Add_bias_act_kernelLauncher
+ * (src/layer/func_wrapper.h:90-94 -> src/cuda/cuda_kernels.cu:71-84,302-319). */
+LIGER_API int liger_add_bias_gelu(void* x, const void* bias, int m, int n, void* stream);
+
+/* {q,k,v}_out[b][h][s][d] = {Q,K,V}[b*S+s][h*D+d] + bias. Replaces Add_QKV_bias_transpose
+ * (src/layer/func_wrapper.h:57-62 -> src/cuda/attention_kernels.cu:133-163,226-329). */
+LIGER_API int liger_add_qkv_bias_transpose(void* q_out, void* k_out, void* v_out, const void* q, const void* bq, const void* k,
+                                 const void* bk, const void* v, const void* bv, int batch, int seq_len, int heads,
+                                 int head_dim, void* stream);
+
+/* dst[b*S+s][h*D+d] = src[b][h][s][d]. Replaces Transpose_kernel
+ * (src/layer/func_wrapper.h:77-81 -> src/cuda/attention_kernels.cu:693-742). */
+LIGER_API int liger_transpose_heads(void* dst, const void* src, int batch, int seq_len, int heads, int head_dim, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LIGER_B200_H */
