@@ -45,7 +45,17 @@ SIGNATURES = {
     "liger_add_bias_gelu": (_I, [_P, _P, _I, _I, _P]),
     "liger_add_qkv_bias_transpose": (_I, [_P] * 9 + [_I] * 4 + [_P]),
     "liger_transpose_heads": (_I, [_P, _P, _I, _I, _I, _I, _P]),
+    "liger_comm_create": (_I, [C.POINTER(_P), _I, _I, _SZ, _I]),
+    "liger_comm_export": (_I, [_P, _P]),
+    "liger_comm_connect": (_I, [_P, _P]),
+    "liger_comm_destroy": (_I, [_P]),
+    "liger_comm_data": (_P, [_P]),
+    "liger_comm_data_bytes": (_SZ, [_P]),
+    "liger_comm_rank": (_I, [_P]),
+    "liger_comm_world_size": (_I, [_P]),
+    "liger_allreduce_fused": (_I, [_P, _I, _SZ, _SZ, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
 }
+COMM_HANDLE_BYTES = 128
 
 _lib = None
 

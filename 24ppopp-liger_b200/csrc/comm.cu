@@ -1,0 +1,393 @@
+// Tensor-parallel communication over NVLink / NVSwitch peer memory.
+//
+// Replaces the reference's NCCL communicator and ncclAllReduce (src/communicator.h:9-41,
+// src/layer/func_wrapper.h:40-43): each rank owns a symmetric segment that every peer maps
+// (CUDA IPC between processes, peer access inside one process), and the all-reduce is a kernel
+// that reads peers' partial sums directly (plain peer loads), reduces in fp32, applies the
+// residual add and LayerNorm that follow the all-reduce in the layer, and stores the finished
+// rows into every peer's segment (plain peer stores).  No NCCL, no multicast objects.
+//
+// Cross-rank synchronisation: per channel, rank r has flags[p] written by peer p.  A barrier with
+// epoch e = "write e into my slot on every peer, then wait until all my slots are >= e".  Epochs
+// are handed out by the host per launch.  Every wait is bounded (common.cuh).
+#include <unistd.h>
+
+#include <cstring>
+#include <vector>
+
+#include "runtime.h"
+
+namespace liger {
+
+constexpr int kMaxRanks = LIGER_COMM_MAX_RANKS;
+constexpr size_t kFlagRegionBytes = 65536;  // flags live in front of the data region
+constexpr int kFlagStrideWords = 32;        // one 128-byte line per (channel, peer) flag
+constexpr int kArThreads = 256;
+constexpr int kArMaxVec = 8;
+
+struct CommDev {
+  uint8_t* base[kMaxRanks];
+  int rank, ws;
+};
+
+struct HandleBlob {
+  uint32_t magic;
+  int32_t rank;
+  int32_t device;
+  int32_t pad;
+  int64_t pid;
+  uint64_t ptr;
+  uint64_t seg_bytes;
+  cudaIpcMemHandle_t ipc;
+};
+static_assert(sizeof(HandleBlob) <= LIGER_COMM_HANDLE_BYTES, "handle blob too large");
+constexpr uint32_t kHandleMagic = 0x4c474843u;
+
+}  // namespace liger
+
+struct liger_comm {
+  int rank = 0, ws = 1, channels = 1, device = 0;
+  size_t data_bytes = 0, seg_bytes = 0;
+  uint8_t* local = nullptr;
+  uint8_t* peer[liger::kMaxRanks] = {};
+  bool ipc_open[liger::kMaxRanks] = {};
+  bool connected = false;
+  std::vector<uint32_t> epoch;   // per channel, host side
+  unsigned int* done = nullptr;  // per channel CTA-completion counters (device)
+};
+
+namespace liger {
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ uint32_t* flag_ptr(uint8_t* seg_base, int channel, int slot) {
+  return reinterpret_cast<uint32_t*>(seg_base) + ((size_t)channel * kMaxRanks + slot) * kFlagStrideWords;
+}
+
+// threads 0..ws-1: publish `epoch` into my slot on every rank (including myself)
+__device__ __forceinline__ void barrier_signal(const CommDev& c, int channel, uint32_t epoch) {
+  if ((int)threadIdx.x < c.ws) st_release_sys(flag_ptr(c.base[threadIdx.x], channel, c.rank), epoch);
+}
+// threads 0..ws-1 poll the local slots; returns false (for the whole CTA) on timeout
+__device__ __forceinline__ bool barrier_wait(const CommDev& c, int channel, uint32_t epoch, int* s_fail,
+                                             DeviceStatus* st, unsigned int where) {
+  if ((int)threadIdx.x < c.ws) {
+    const uint32_t* f = flag_ptr(c.base[c.rank], channel, threadIdx.x);
+    const unsigned long long t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while ((int32_t)(ld_acquire_sys(f) - epoch) < 0) {
+      if ((++spins & 0xffu) == 0 && globaltimer_ns() - t0 > kWaitBudgetNs) {
+        *s_fail = 1;
+        report_failure(st, LIGER_DEV_TIMEOUT, where, (unsigned)threadIdx.x, epoch);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  return *s_fail == 0;
+}
+
+__global__ void __launch_bounds__(kArThreads)
+allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t out_off, __half* __restrict__ hidden,
+                       const __half* __restrict__ bias, const __half* __restrict__ gamma,
+                       const __half* __restrict__ beta, int n, int row_lo, int row_hi, int one_shot, uint32_t epoch_in,
+                       uint32_t epoch_out, unsigned int* done_counter, DeviceStatus* st) {
+  __shared__ float red[32];
+  __shared__ int s_fail;
+  __shared__ int s_last;
+  if (threadIdx.x == 0) { s_fail = 0; s_last = 0; }
+  __syncthreads();
+
+  // ---- entry barrier: every rank's partial is complete and visible ----
+  if (blockIdx.x == 0) barrier_signal(c, channel, epoch_in);
+  if (!barrier_wait(c, channel, epoch_in, &s_fail, st, 0x200u)) return;
+
+  const int nvec = n >> 3;
+  for (int row = row_lo + blockIdx.x; row < row_hi; row += gridDim.x) {
+    const size_t roff = (size_t)row * n;
+    float v[kArMaxVec][8];
+#pragma unroll
+    for (int i = 0; i < kArMaxVec; ++i)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[i][j] = 0.0f;
+    for (int kx = 0; kx < c.ws; ++kx) {
+      int p = c.rank + kx;
+      if (p >= c.ws) p -= c.ws;
+      const __half* src = reinterpret_cast<const __half*>(c.base[p] + partial_off) + roff;
+#pragma unroll
+      for (int i = 0; i < kArMaxVec; ++i) {
+        const int idx = threadIdx.x + i * kArThreads;
+        if (idx < nvec) {
+          uint4 u = __ldcg(reinterpret_cast<const uint4*>(src + (size_t)idx * 8));
+          const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float2 f = __half22float2(h[j]);
+            v[i][2 * j] += f.x;
+            v[i][2 * j + 1] += f.y;
+          }
+        }
+      }
+    }
+    // residual + bias; round to fp16 (the value every later consumer sees)
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kArMaxVec; ++i) {
+      const int idx = threadIdx.x + i * kArThreads;
+      if (idx < nvec) {
+        if (hidden != nullptr) {
+          uint4 r = *reinterpret_cast<const uint4*>(hidden + roff + (size_t)idx * 8);
+          const __half2* rh = reinterpret_cast<const __half2*>(&r);
+          uint4 bu = bias ? __ldg(reinterpret_cast<const uint4*>(bias + (size_t)idx * 8)) : make_uint4(0, 0, 0, 0);
+          const __half2* bh = reinterpret_cast<const __half2*>(&bu);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float2 f = __half22float2(rh[j]);
+            float2 b = __half22float2(bh[j]);
+            v[i][2 * j] += f.x + b.x;
+            v[i][2 * j + 1] += f.y + b.y;
+          }
+        }
+        uint4 o;
+        uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          sum += v[i][2 * j] + v[i][2 * j + 1];
+          __half2 hh = __floats2half2_rn(v[i][2 * j], v[i][2 * j + 1]);
+          ow[j] = *reinterpret_cast<uint32_t*>(&hh);
+          float2 back = __half22float2(hh);
+          v[i][2 * j] = back.x;
+          v[i][2 * j + 1] = back.y;
+        }
+        if (hidden != nullptr) *reinterpret_cast<uint4*>(hidden + roff + (size_t)idx * 8) = o;
+      }
+    }
+    float mean = 0.0f, rstd = 1.0f;
+    if (gamma != nullptr) {
+      // two-pass statistics as in the reference's LayerNorm (src/cuda/cuda_kernels.cu:463-508)
+      sum = warp_sum(sum);
+      __syncthreads();
+      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sum;
+      __syncthreads();
+      float t = (threadIdx.x & 31) < (kArThreads >> 5) ? red[threadIdx.x & 31] : 0.0f;
+      mean = warp_sum(t) / (float)n;
+      float vs = 0.0f;
+#pragma unroll
+      for (int i = 0; i < kArMaxVec; ++i) {
+        const int idx = threadIdx.x + i * kArThreads;
+        if (idx < nvec) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { float d = v[i][j] - mean; vs += d * d; }
+        }
+      }
+      vs = warp_sum(vs);
+      __syncthreads();
+      if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = vs;
+      __syncthreads();
+      t = (threadIdx.x & 31) < (kArThreads >> 5) ? red[threadIdx.x & 31] : 0.0f;
+      rstd = rsqrtf(warp_sum(t) / (float)n + 1e-6f);
+    }
+#pragma unroll
+    for (int i = 0; i < kArMaxVec; ++i) {
+      const int idx = threadIdx.x + i * kArThreads;
+      if (idx < nvec) {
+        uint4 o;
+        uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+        if (gamma != nullptr) {
+          uint4 gu = __ldg(reinterpret_cast<const uint4*>(gamma + (size_t)idx * 8));
+          uint4 bu = __ldg(reinterpret_cast<const uint4*>(beta + (size_t)idx * 8));
+          const __half2* gh = reinterpret_cast<const __half2*>(&gu);
+          const __half2* bh = reinterpret_cast<const __half2*>(&bu);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float2 g = __half22float2(gh[j]);
+            float2 b = __half22float2(bh[j]);
+            ow[j] = pack_half2((v[i][2 * j] - mean) * rstd * g.x + b.x, (v[i][2 * j + 1] - mean) * rstd * g.y + b.y);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) ow[j] = pack_half2(v[i][2 * j], v[i][2 * j + 1]);
+        }
+        if (one_shot) {
+          *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(c.base[c.rank] + out_off) + roff + (size_t)idx * 8) = o;
+        } else {
+          for (int kx = 0; kx < c.ws; ++kx) {
+            int p = c.rank + kx;
+            if (p >= c.ws) p -= c.ws;
+            *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(c.base[p] + out_off) + roff + (size_t)idx * 8) = o;
+          }
+        }
+      }
+    }
+  }
+
+  // ---- exit barrier: all of this rank's stores are visible before any rank moves on ----
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int ticket = atomicAdd(done_counter, 1u);
+    if (ticket == gridDim.x - 1) { *done_counter = 0u; s_last = 1; }
+  }
+  __syncthreads();
+  if (s_last) {
+    __threadfence_system();
+    barrier_signal(c, channel, epoch_out);
+    barrier_wait(c, channel, epoch_out, &s_fail, st, 0x201u);
+  }
+}
+
+}  // namespace liger
+
+using namespace liger;
+
+extern "C" int liger_comm_create(liger_comm** out, int rank, int world_size, size_t data_bytes, int channels) {
+  if (!out || world_size < 1 || world_size > kMaxRanks || rank < 0 || rank >= world_size || channels < 1 ||
+      (size_t)channels * kMaxRanks * kFlagStrideWords * 4 > kFlagRegionBytes)
+    return set_error(LIGER_ERR_INVALID, "comm_create: bad argument (world_size <= %d, channels <= %d)", kMaxRanks,
+                     (int)(kFlagRegionBytes / (kMaxRanks * kFlagStrideWords * 4)));
+  const DeviceInfo* dev = current_device();
+  if (!dev) return LIGER_ERR_CUDA;
+  liger_comm* c = new liger_comm();
+  c->rank = rank; c->ws = world_size; c->channels = channels; c->device = dev->device;
+  c->data_bytes = (data_bytes + 255) & ~(size_t)255;
+  c->seg_bytes = kFlagRegionBytes + c->data_bytes;
+  cudaError_t e = cudaMalloc((void**)&c->local, c->seg_bytes);
+  if (e == cudaSuccess) e = cudaMemset(c->local, 0, kFlagRegionBytes);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&c->done, sizeof(unsigned int) * channels);
+  if (e == cudaSuccess) e = cudaMemset(c->done, 0, sizeof(unsigned int) * channels);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    if (c->local) cudaFree(c->local);
+    if (c->done) cudaFree(c->done);
+    delete c;
+    return set_error(LIGER_ERR_CUDA, "comm_create: allocating %zu bytes failed: %s", data_bytes, cudaGetErrorString(e));
+  }
+  c->epoch.assign(channels, 0u);
+  c->peer[rank] = c->local;
+  if (world_size == 1) c->connected = true;
+  *out = c;
+  return LIGER_OK;
+}
+
+extern "C" int liger_comm_export(liger_comm* c, void* handle_out) {
+  if (!c || !handle_out) return set_error(LIGER_ERR_INVALID, "comm_export: null argument");
+  HandleBlob b;
+  memset(&b, 0, sizeof(b));
+  b.magic = kHandleMagic; b.rank = c->rank; b.device = c->device; b.pid = (int64_t)getpid();
+  b.ptr = (uint64_t)(uintptr_t)c->local; b.seg_bytes = c->seg_bytes;
+  if (c->ws > 1) {
+    cudaError_t e = cudaIpcGetMemHandle(&b.ipc, c->local);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return set_error(LIGER_ERR_COMM, "cudaIpcGetMemHandle: %s", cudaGetErrorString(e));
+    }
+  }
+  memset(handle_out, 0, LIGER_COMM_HANDLE_BYTES);
+  memcpy(handle_out, &b, sizeof(b));
+  return LIGER_OK;
+}
+
+extern "C" int liger_comm_connect(liger_comm* c, const void* all_handles) {
+  if (!c || !all_handles) return set_error(LIGER_ERR_INVALID, "comm_connect: null argument");
+  LIGER_CUDA_TRY(cudaSetDevice(c->device));
+  for (int p = 0; p < c->ws; ++p) {
+    HandleBlob b;
+    memcpy(&b, (const uint8_t*)all_handles + (size_t)p * LIGER_COMM_HANDLE_BYTES, sizeof(b));
+    if (b.magic != kHandleMagic || b.rank != p)
+      return set_error(LIGER_ERR_COMM, "comm_connect: handle %d is malformed (magic %08x, rank %d)", p, b.magic, b.rank);
+    if (b.seg_bytes != c->seg_bytes)
+      return set_error(LIGER_ERR_COMM, "comm_connect: rank %d segment is %llu bytes, mine is %zu", p,
+                       (unsigned long long)b.seg_bytes, c->seg_bytes);
+    if (p == c->rank) continue;
+    if (b.pid == (int64_t)getpid()) {
+      if (b.device != c->device) {
+        int can = 0;
+        LIGER_CUDA_TRY(cudaDeviceCanAccessPeer(&can, c->device, b.device));
+        if (!can) return set_error(LIGER_ERR_COMM, "comm_connect: device %d cannot access device %d", c->device, b.device);
+        cudaError_t e = cudaDeviceEnablePeerAccess(b.device, 0);
+        if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled)
+          return set_error(LIGER_ERR_COMM, "cudaDeviceEnablePeerAccess(%d): %s", b.device, cudaGetErrorString(e));
+        cudaGetLastError();
+      }
+      c->peer[p] = (uint8_t*)(uintptr_t)b.ptr;
+    } else {
+      void* ptr = nullptr;
+      cudaError_t e = cudaIpcOpenMemHandle(&ptr, b.ipc, cudaIpcMemLazyEnablePeerAccess);
+      if (e != cudaSuccess) {
+        cudaGetLastError();
+        return set_error(LIGER_ERR_COMM, "cudaIpcOpenMemHandle(rank %d): %s", p, cudaGetErrorString(e));
+      }
+      c->peer[p] = (uint8_t*)ptr;
+      c->ipc_open[p] = true;
+    }
+  }
+  c->connected = true;
+  return LIGER_OK;
+}
+
+extern "C" int liger_comm_destroy(liger_comm* c) {
+  if (!c) return LIGER_OK;
+  cudaSetDevice(c->device);
+  cudaDeviceSynchronize();
+  for (int p = 0; p < c->ws; ++p)
+    if (c->ipc_open[p]) cudaIpcCloseMemHandle(c->peer[p]);
+  if (c->local) cudaFree(c->local);
+  if (c->done) cudaFree(c->done);
+  delete c;
+  cudaGetLastError();
+  return LIGER_OK;
+}
+
+extern "C" void* liger_comm_data(liger_comm* c) { return c ? c->local + kFlagRegionBytes : nullptr; }
+extern "C" size_t liger_comm_data_bytes(liger_comm* c) { return c ? c->data_bytes : 0; }
+extern "C" int liger_comm_rank(liger_comm* c) { return c ? c->rank : -1; }
+extern "C" int liger_comm_world_size(liger_comm* c) { return c ? c->ws : 0; }
+
+extern "C" int liger_allreduce_fused(liger_comm* c, int channel, size_t partial_off, size_t out_off, void* hidden,
+                                     const void* bias, const void* gamma, const void* beta, int m, int n, int row_begin,
+                                     int row_end, int one_shot, void* stream) {
+  if (!c) return set_error(LIGER_ERR_INVALID, "allreduce_fused: null communicator");
+  if (!c->connected) return set_error(LIGER_ERR_COMM, "allreduce_fused: communicator is not connected");
+  if (channel < 0 || channel >= c->channels) return set_error(LIGER_ERR_INVALID, "allreduce_fused: channel %d of %d", channel, c->channels);
+  if (m <= 0 || n <= 0 || n % 8 || n > kArThreads * kArMaxVec * 8)
+    return set_error(LIGER_ERR_UNSUPPORTED, "allreduce_fused: n = %d must be a multiple of 8 and <= %d", n,
+                     kArThreads * kArMaxVec * 8);
+  if (row_begin < 0 || row_end > m || row_begin > row_end) return set_error(LIGER_ERR_INVALID, "allreduce_fused: bad row range");
+  const size_t bytes = (size_t)m * n * 2;
+  if (partial_off % 16 || out_off % 16 || partial_off + bytes > c->data_bytes || out_off + bytes > c->data_bytes)
+    return set_error(LIGER_ERR_INVALID, "allreduce_fused: offsets must be 16-byte aligned and inside the %zu-byte data region",
+                     c->data_bytes);
+  if ((gamma == nullptr) != (beta == nullptr)) return set_error(LIGER_ERR_INVALID, "allreduce_fused: gamma and beta go together");
+  if (((uintptr_t)hidden | (uintptr_t)bias | (uintptr_t)gamma | (uintptr_t)beta) & 15u)
+    return set_error(LIGER_ERR_INVALID, "allreduce_fused: pointers must be 16-byte aligned");
+  const DeviceInfo* dev = current_device();
+  if (!dev) return LIGER_ERR_CUDA;
+  CommDev cd;
+  for (int p = 0; p < kMaxRanks; ++p) cd.base[p] = p < c->ws ? c->peer[p] : nullptr;
+  cd.rank = c->rank; cd.ws = c->ws;
+  int lo = row_begin, hi = row_end;
+  if (!one_shot) {
+    const int rpr = (m + c->ws - 1) / c->ws;
+    lo = row_begin > c->rank * rpr ? row_begin : c->rank * rpr;
+    const int own_hi = (c->rank + 1) * rpr < m ? (c->rank + 1) * rpr : m;
+    hi = row_end < own_hi ? row_end : own_hi;
+    if (hi < lo) hi = lo;
+  }
+  int grid = hi - lo;
+  const int cap = dev->sm_count * 4;
+  if (grid > cap) grid = cap;
+  if (grid < 1) grid = 1;
+  const uint32_t e_in = ++c->epoch[channel];
+  const uint32_t e_out = ++c->epoch[channel];
+  allreduce_fused_kernel<<<grid, kArThreads, 0, (cudaStream_t)stream>>>(
+      cd, channel, kFlagRegionBytes + partial_off, kFlagRegionBytes + out_off, (__half*)hidden, (const __half*)bias,
+      (const __half*)gamma, (const __half*)beta, n, lo, hi, one_shot, e_in, e_out, c->done + channel, dev->status_dev);
+  return check_launch("allreduce_fused_kernel");
+}

@@ -188,6 +188,64 @@ LIGER_API int liger_add_qkv_bias_transpose(void* q_out, void* k_out, void* v_out
  * (src/layer/func_wrapper.h:77-81 -> src/cuda/attention_kernels.cu:693-742). */
 LIGER_API int liger_transpose_heads(void* dst, const void* src, int batch, int seq_len, int heads, int head_dim, void* stream);
 
+/* ------------------------------------------------------------------------------------------ */
+/* Tensor-parallel communication over NVLink / NVSwitch peer memory                           */
+/* ------------------------------------------------------------------------------------------ */
+
+/*
+ * A communicator owns one "symmetric segment" per rank: a device buffer of the same size on every
+ * GPU that every peer maps, so kernels address peer memory directly by (rank, offset).  It
+ * replaces the reference's NCCL communicator (createNcclComm, src/communicator.h:9-41: the
+ * ncclUniqueId broadcast becomes an exchange of LIGER_COMM_HANDLE_BYTES-byte handles over
+ * whatever the host already uses -- MPI_Bcast / all-gather, a torch.distributed group ...).
+ *
+ *   liger_comm_create   allocate the local segment (data_bytes + flag words), one process per GPU
+ *   liger_comm_export   write this rank's handle
+ *   liger_comm_connect  given all ranks' handles (rank order), map every peer's segment
+ *
+ * Ranks that live in one process (several GPUs driven by one host thread each) are detected by
+ * process id and mapped with peer access instead of IPC handles.  world_size <= 8.
+ * `channels` independent flag sets let collectives of different in-flight requests proceed
+ * without sharing barrier state; all ranks must launch the collectives of one channel in the
+ * same order.
+ */
+typedef struct liger_comm liger_comm;
+#define LIGER_COMM_HANDLE_BYTES 128
+#define LIGER_COMM_MAX_RANKS 8
+
+LIGER_API int liger_comm_create(liger_comm** out, int rank, int world_size, size_t data_bytes, int channels);
+LIGER_API int liger_comm_export(liger_comm* comm, void* handle_out);
+LIGER_API int liger_comm_connect(liger_comm* comm, const void* all_handles);
+LIGER_API int liger_comm_destroy(liger_comm* comm);
+/* Base address of this rank's data region (offsets below are bytes from this base). */
+LIGER_API void* liger_comm_data(liger_comm* comm);
+LIGER_API size_t liger_comm_data_bytes(liger_comm* comm);
+LIGER_API int liger_comm_rank(liger_comm* comm);
+LIGER_API int liger_comm_world_size(liger_comm* comm);
+
+/*
+ * All-reduce (sum over ranks) of the row-parallel partials, fused with what follows it in the layer.
+ * Replaces Allreduce (src/layer/func_wrapper.h:40-43, bound at src/layer/linear.h:55-60) together
+ * with the residual / LayerNorm kernel after it (Layer_Norm, src/layer/func_wrapper.h:110-114, or
+ * add_bias_input_layernorm_2, src/cuda/cuda_kernels.cu:360-409).
+ *
+ * Every rank holds its partial [M, N] fp16 at byte offset partial_off of its segment.  Rank r owns
+ * rows [r*ceil(M/ws), (r+1)*ceil(M/ws)).  For each owned row in [row_begin, row_end):
+ *     t = sum_p partial_p[row]            fp32; order: own partial first, then increasing rank, cyclic
+ *     if hidden:  t += hidden[row] + bias ; hidden[row] = fp16(t)   (residual stream, local, owner rows)
+ *     if gamma:   o = LayerNorm(fp16(t)) * gamma + beta   else   o = fp16(t)
+ *     store o to row `row` of the [M, N] tensor at byte offset out_off of EVERY rank's segment
+ * preceded and followed by a cross-rank barrier on flag set `channel`, so that a kernel launched
+ * after this one on the same stream sees all rows.  With one_shot != 0 every rank instead reduces
+ * all rows itself and stores only locally (latency-bound sizes; hidden is then updated for all
+ * rows on every rank).  Waits on peers are bounded; on timeout the device status word is set.
+ * N % 8 == 0, N <= 16384.  row_begin / row_end allow the collective to be issued in slices
+ * (decompose_comm_callback, src/utils.h:262-281).
+ */
+LIGER_API int liger_allreduce_fused(liger_comm* comm, int channel, size_t partial_off, size_t out_off, void* hidden,
+                                    const void* bias, const void* gamma, const void* beta, int m, int n, int row_begin,
+                                    int row_end, int one_shot, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
