@@ -9,6 +9,6 @@ compute entry point fails without a CUDA device.
 """
 from . import capi
 from .build import build_all, LIB_PATH
-from .capi import lib, check, LigerError, GemmArgs
+from .capi import lib, check, LigerError, GemmArgs, ModelConfig, default_config
 
-__all__ = ["capi", "build_all", "LIB_PATH", "lib", "check", "LigerError", "GemmArgs"]
+__all__ = ["capi", "build_all", "LIB_PATH", "lib", "check", "LigerError", "GemmArgs", "ModelConfig", "default_config"]

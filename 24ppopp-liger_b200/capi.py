@@ -23,10 +23,45 @@ class GemmArgs(C.Structure):
         ("lda", C.c_int), ("ldw", C.c_int), ("ldc", C.c_int), ("ldr", C.c_int),
         ("n_begin", C.c_int), ("n_end", C.c_int), ("epilogue", C.c_int),
         ("seq_len", C.c_int), ("heads", C.c_int), ("head_dim", C.c_int),
+        ("kv_stride", C.c_int), ("kv_pos", C.c_int),
     ]
 
 
 _P, _I, _F, _U32, _SZ = C.c_void_p, C.c_int, C.c_float, C.c_uint32, C.c_size_t
+
+
+class ModelConfig(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("max_batch_size", "max_seq_len", "head_num", "size_per_head", "layer_num",
+                                       "kernel_num", "factor", "rq_interval", "graph", "act", "ffn_inner", "causal")] + \
+               [("seed", C.c_uint32), ("num_requests", C.c_int), ("ignore_num", C.c_int), ("schedule_deep", C.c_int),
+                ("contention", C.c_float), ("poisson", C.c_int), ("min_seq_len", C.c_int), ("seq_round", C.c_int),
+                ("workspace_slots", C.c_int), ("kv_capacity", C.c_int)]
+
+
+class ServingMetrics(C.Structure):
+    _fields_ = [("records", C.c_int), ("launch_errors", C.c_int), ("total_duration_ms", C.c_double),
+                ("throughput_samples_s", C.c_double), ("average_latency_ms", C.c_double), ("tokens_per_s", C.c_double),
+                ("p50_latency_ms", C.c_double), ("p99_latency_ms", C.c_double), ("mean_gpu_ms", C.c_double),
+                ("tokens", C.c_longlong), ("segments", C.c_longlong), ("secondary_launches", C.c_longlong),
+                ("decompositions", C.c_longlong)]
+
+
+class SimKernel(C.Structure):
+    _fields_ = [("type", C.c_int), ("duration_ms", C.c_float)]
+
+
+class SimLaunch(C.Structure):
+    _fields_ = [("request", C.c_int), ("layer", C.c_int), ("name", C.c_int), ("stream", C.c_int),
+                ("units_begin", C.c_int), ("units_end", C.c_int), ("duration_ms", C.c_float),
+                ("t_start_ms", C.c_double), ("t_end_ms", C.c_double)]
+
+
+BCAST_INT_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.POINTER(C.c_int))
+BARRIER_FN = C.CFUNCTYPE(C.c_int, C.c_void_p)
+MODE_PROFILE, MODE_SCHEDULE, MODE_NO_SCHEDULE = 0, 1, 2
+GRAPH_REF, GRAPH_PRELN = 0, 1
+ACT_GELU, ACT_GEGLU = 0, 1
+COMMUNICATION, COMPUTATION, GEMM = 0, 1, 2
 
 # name -> (restype, argtypes); must list every function declared in include/liger_b200.h
 SIGNATURES = {
@@ -53,9 +88,30 @@ SIGNATURES = {
     "liger_comm_data_bytes": (_SZ, [_P]),
     "liger_comm_rank": (_I, [_P]),
     "liger_comm_world_size": (_I, [_P]),
-    "liger_allreduce_fused": (_I, [_P, _I, _SZ, _SZ, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
+    "liger_allreduce_fused": (_I, [_P, _I, _SZ, _SZ, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
+    "liger_model_config_init": (None, [C.POINTER(ModelConfig)]),
+    "liger_model_comm_bytes": (_SZ, [C.POINTER(ModelConfig), _I]),
+    "liger_model_create": (_I, [C.POINTER(_P), C.POINTER(ModelConfig), _I, _I, _P]),
+    "liger_model_destroy": (_I, [_P]),
+    "liger_model_forward": (_I, [_P, _P, _P, _I, _I, _I, _P]),
+    "liger_model_forward_host": (_I, [_P, _P, _P, _I, _I, _I, _P]),
+    "liger_model_set_mask": (_I, [_P, _P]),
+    "liger_serve": (_I, [_P, _I, BCAST_INT_FN, BARRIER_FN, _P, C.c_char_p, _I, C.POINTER(ServingMetrics)]),
+    "liger_sim_serve": (_I, [C.POINTER(ModelConfig), C.POINTER(SimKernel), _I, _I, C.c_double, C.c_double,
+                             C.POINTER(SimLaunch), _I, C.POINTER(_I), C.POINTER(ServingMetrics)]),
 }
 COMM_HANDLE_BYTES = 128
+
+
+def default_config(**kw):
+    """ModelConfig with the reference's defaults (src/main.cu:14-21), overridden by keyword."""
+    cfg = ModelConfig()
+    lib().liger_model_config_init(C.byref(cfg))
+    for k, v in kw.items():
+        if not hasattr(cfg, k):
+            raise AttributeError(k)
+        setattr(cfg, k, v)
+    return cfg
 
 _lib = None
 

@@ -95,7 +95,8 @@ __device__ __forceinline__ bool barrier_wait(const CommDev& c, int channel, uint
 }
 
 __global__ void __launch_bounds__(kArThreads)
-allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t out_off, __half* __restrict__ hidden,
+allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t out_off,
+                       const __half* residual_in, __half* hidden,
                        const __half* __restrict__ bias, const __half* __restrict__ gamma,
                        const __half* __restrict__ beta, int n, int row_lo, int row_hi, int one_shot, uint32_t epoch_in,
                        uint32_t epoch_out, unsigned int* done_counter, DeviceStatus* st) {
@@ -143,7 +144,7 @@ allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t out_of
       const int idx = threadIdx.x + i * kArThreads;
       if (idx < nvec) {
         if (hidden != nullptr) {
-          uint4 r = *reinterpret_cast<const uint4*>(hidden + roff + (size_t)idx * 8);
+          uint4 r = *reinterpret_cast<const uint4*>(residual_in + roff + (size_t)idx * 8);
           const __half2* rh = reinterpret_cast<const __half2*>(&r);
           uint4 bu = bias ? __ldg(reinterpret_cast<const uint4*>(bias + (size_t)idx * 8)) : make_uint4(0, 0, 0, 0);
           const __half2* bh = reinterpret_cast<const __half2*>(&bu);
@@ -350,8 +351,8 @@ extern "C" size_t liger_comm_data_bytes(liger_comm* c) { return c ? c->data_byte
 extern "C" int liger_comm_rank(liger_comm* c) { return c ? c->rank : -1; }
 extern "C" int liger_comm_world_size(liger_comm* c) { return c ? c->ws : 0; }
 
-extern "C" int liger_allreduce_fused(liger_comm* c, int channel, size_t partial_off, size_t out_off, void* hidden,
-                                     const void* bias, const void* gamma, const void* beta, int m, int n, int row_begin,
+extern "C" int liger_allreduce_fused(liger_comm* c, int channel, size_t partial_off, size_t out_off,
+                                     const void* residual_in, void* hidden, const void* bias, const void* gamma, const void* beta, int m, int n, int row_begin,
                                      int row_end, int one_shot, void* stream) {
   if (!c) return set_error(LIGER_ERR_INVALID, "allreduce_fused: null communicator");
   if (!c->connected) return set_error(LIGER_ERR_COMM, "allreduce_fused: communicator is not connected");
@@ -365,7 +366,8 @@ extern "C" int liger_allreduce_fused(liger_comm* c, int channel, size_t partial_
     return set_error(LIGER_ERR_INVALID, "allreduce_fused: offsets must be 16-byte aligned and inside the %zu-byte data region",
                      c->data_bytes);
   if ((gamma == nullptr) != (beta == nullptr)) return set_error(LIGER_ERR_INVALID, "allreduce_fused: gamma and beta go together");
-  if (((uintptr_t)hidden | (uintptr_t)bias | (uintptr_t)gamma | (uintptr_t)beta) & 15u)
+  if (hidden && !residual_in) residual_in = hidden;
+  if (((uintptr_t)hidden | (uintptr_t)residual_in | (uintptr_t)bias | (uintptr_t)gamma | (uintptr_t)beta) & 15u)
     return set_error(LIGER_ERR_INVALID, "allreduce_fused: pointers must be 16-byte aligned");
   const DeviceInfo* dev = current_device();
   if (!dev) return LIGER_ERR_CUDA;
@@ -387,7 +389,7 @@ extern "C" int liger_allreduce_fused(liger_comm* c, int channel, size_t partial_
   const uint32_t e_in = ++c->epoch[channel];
   const uint32_t e_out = ++c->epoch[channel];
   allreduce_fused_kernel<<<grid, kArThreads, 0, (cudaStream_t)stream>>>(
-      cd, channel, kFlagRegionBytes + partial_off, kFlagRegionBytes + out_off, (__half*)hidden, (const __half*)bias,
+      cd, channel, kFlagRegionBytes + partial_off, kFlagRegionBytes + out_off, (const __half*)residual_in, (__half*)hidden, (const __half*)bias,
       (const __half*)gamma, (const __half*)beta, n, lo, hi, one_shot, e_in, e_out, c->done + channel, dev->status_dev);
   return check_launch("allreduce_fused_kernel");
 }

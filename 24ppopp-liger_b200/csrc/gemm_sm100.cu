@@ -31,6 +31,7 @@ struct GemmParams {
   int ldc, ldr;
   int epilogue;
   int seq_len, heads, head_dim;
+  int kv_stride, kv_pos;
   int tiles_m, tiles_n, kblocks;
   DeviceStatus* status;
 };
@@ -94,7 +95,10 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, int row, int
       const int d = rem - head * p.head_dim;
       const int b = row / p.seq_len;
       const int s = row - b * p.seq_len;
-      dst = p.qkv[which] + (((size_t)b * p.heads + head) * p.seq_len + s) * p.head_dim + d;
+      if (which != 0 && p.kv_stride > 0)
+        dst = p.qkv[which] + (((size_t)b * p.heads + head) * p.kv_stride + p.kv_pos + s) * p.head_dim + d;
+      else
+        dst = p.qkv[which] + (((size_t)b * p.heads + head) * p.seq_len + s) * p.head_dim + d;
     } else {
       dst = p.c + (size_t)row * p.ldc + col;
     }
@@ -347,7 +351,10 @@ extern "C" int liger_gemm_fp16(const liger_gemm_args* args, void* stream) {
       if (((uintptr_t)a.q_out | (uintptr_t)a.k_out | (uintptr_t)a.v_out) & 15u)
         return set_error(LIGER_ERR_INVALID, "gemm: q/k/v outputs must be 16-byte aligned");
       p.qkv[0] = (__half*)a.q_out; p.qkv[1] = (__half*)a.k_out; p.qkv[2] = (__half*)a.v_out;
+      if (a.kv_stride < 0 || a.kv_pos < 0 || (a.kv_stride > 0 && a.kv_pos + a.seq_len > a.kv_stride))
+        return set_error(LIGER_ERR_INVALID, "gemm: kv_pos + seq_len must fit in kv_stride");
       p.seq_len = a.seq_len; p.heads = a.heads; p.head_dim = a.head_dim;
+      p.kv_stride = a.kv_stride; p.kv_pos = a.kv_pos;
       break;
     default:
       return set_error(LIGER_ERR_INVALID, "gemm: unknown epilogue %d", a.epilogue);

@@ -1,0 +1,293 @@
+// C ABI over the host-side runtime (host/*.h): model construction and forward pass, the three
+// serving entry points, and the scheduler on a simulated device.
+#define LIGER_HOST_WITH_CUDA 1
+#include <memory>
+#include <string>
+
+#include "../host/layers.h"
+#include "../host/profile_io.h"
+#include "../host/runtime_iface.h"
+#include "../host/sample.h"
+#include "../host/scheduler.h"
+#include "../host/test_schedule.h"
+#include "runtime.h"
+
+using namespace liger_host;
+
+struct liger_model {
+  BertInitParam bp;
+  StaticNvInitParam sp;
+  Bert_Model* model = nullptr;
+  half_t* io_in = nullptr;   // device staging for the host-buffer entry point
+  half_t* io_out = nullptr;
+  int device = 0;
+};
+
+namespace {
+
+BertInitParam to_params(const liger_model_config& c) {
+  BertInitParam bp(c.max_batch_size, c.max_seq_len, c.head_num, c.size_per_head, c.layer_num, c.kernel_num, c.factor,
+                   c.rq_interval);
+  bp.graph = c.graph; bp.act = c.act; bp.ffn_inner = c.ffn_inner; bp.causal = c.causal; bp.seed = c.seed;
+  bp.num_requests = c.num_requests; bp.ignore_num = c.ignore_num; bp.schedule_deep = c.schedule_deep;
+  bp.contention = c.contention; bp.poisson = c.poisson; bp.min_seq_len = c.min_seq_len; bp.seq_round = c.seq_round;
+  bp.workspace_slots = c.workspace_slots; bp.kv_capacity = c.kv_capacity;
+  return bp;
+}
+
+int validate(const liger_model_config* c) {
+  if (!c) return liger::set_error(LIGER_ERR_INVALID, "null configuration");
+  if (c->max_batch_size < 1 || c->max_seq_len < 1 || c->head_num < 1 || c->size_per_head < 1 || c->layer_num < 1 ||
+      c->factor < 1 || c->workspace_slots < 1 || c->schedule_deep < 1)
+    return liger::set_error(LIGER_ERR_INVALID, "configuration: sizes must be positive");
+  if (c->schedule_deep + 1 > c->workspace_slots)
+    return liger::set_error(LIGER_ERR_INVALID, "configuration: workspace_slots must be at least schedule_deep + 1");
+  return LIGER_OK;
+}
+
+class CallbackCoordinator : public Coordinator {
+ public:
+  CallbackCoordinator(int rank, int size, liger_bcast_int_fn b, liger_barrier_fn bar, void* ctx)
+      : rank_(rank), size_(size), bcast_(b), barrier_(bar), ctx_(ctx) {}
+  int rank() const override { return rank_; }
+  int size() const override { return size_; }
+  int broadcast_int(int v) override { if (bcast_) bcast_(ctx_, &v); return v; }
+  void barrier() override { if (barrier_) barrier_(ctx_); }
+ private:
+  int rank_, size_;
+  liger_bcast_int_fn bcast_;
+  liger_barrier_fn barrier_;
+  void* ctx_;
+};
+
+void fill_metrics(liger_serving_metrics* out, const ServingMetrics& m, long segments, long secondary, long decomp) {
+  if (!out) return;
+  out->records = m.records; out->launch_errors = m.launch_errors;
+  out->total_duration_ms = m.total_duration_ms; out->throughput_samples_s = m.throughput_samples_s;
+  out->average_latency_ms = m.average_latency_ms; out->tokens_per_s = m.tokens_per_s;
+  out->p50_latency_ms = m.p50_latency_ms; out->p99_latency_ms = m.p99_latency_ms; out->mean_gpu_ms = m.mean_gpu_ms;
+  out->tokens = m.tokens; out->segments = segments; out->secondary_launches = secondary; out->decompositions = decomp;
+}
+
+}  // namespace
+
+extern "C" void liger_model_config_init(liger_model_config* c) {
+  if (!c) return;
+  BertInitParam d;
+  c->max_batch_size = d.max_batch_size; c->max_seq_len = d.max_seq_len; c->head_num = d.head_num;
+  c->size_per_head = d.size_per_head; c->layer_num = d.layer_num; c->kernel_num = d.kernel_num; c->factor = d.factor;
+  c->rq_interval = d.rq_interval; c->graph = d.graph; c->act = d.act; c->ffn_inner = d.ffn_inner; c->causal = d.causal;
+  c->seed = d.seed; c->num_requests = d.num_requests; c->ignore_num = d.ignore_num; c->schedule_deep = d.schedule_deep;
+  c->contention = d.contention; c->poisson = d.poisson; c->min_seq_len = d.min_seq_len; c->seq_round = d.seq_round;
+  c->workspace_slots = d.workspace_slots; c->kv_capacity = d.kv_capacity;
+}
+
+extern "C" size_t liger_model_comm_bytes(const liger_model_config* cfg, int world_size) {
+  if (!cfg || world_size <= 1) return 0;
+  return Bert_Model::comm_bytes_needed(to_params(*cfg));
+}
+
+extern "C" int liger_model_create(liger_model** out, const liger_model_config* cfg, int rank, int world_size,
+                                  liger_comm* comm) {
+  if (!out) return liger::set_error(LIGER_ERR_INVALID, "model_create: null output");
+  int rc = validate(cfg);
+  if (rc != LIGER_OK) return rc;
+  if (world_size < 1 || rank < 0 || rank >= world_size) return liger::set_error(LIGER_ERR_INVALID, "model_create: bad rank / world_size");
+  const liger::DeviceInfo* dev;
+  if ((rc = liger::require_sm100(&dev)) != LIGER_OK) return rc;
+  liger_model* m = new liger_model();
+  m->bp = to_params(*cfg);
+  m->sp = StaticNvInitParam(rank, world_size, comm, 1);
+  m->device = dev->device;
+  try {
+    m->model = new Bert_Model(m->bp, m->sp);
+    const size_t n = m->model->tokens_max() * m->model->H;
+    m->io_in = device_alloc<half_t>(n, "io_in");
+    m->io_out = device_alloc<half_t>(n, "io_out");
+  } catch (const std::exception& e) {
+    delete m;
+    return liger::set_error(LIGER_ERR_CUDA, "model_create: %s", e.what());
+  }
+  *out = m;
+  return LIGER_OK;
+}
+
+extern "C" int liger_model_destroy(liger_model* m) {
+  // Device memory of a model lives until the process exits, as in the reference (its layers have no
+  // destructors); only the host object is released here.
+  delete m;
+  return LIGER_OK;
+}
+
+extern "C" int liger_model_forward(liger_model* m, const void* input, void* output, int batch, int seq_len, int slot,
+                                   void* stream) {
+  if (!m || !input || !output) return liger::set_error(LIGER_ERR_INVALID, "model_forward: null argument");
+  try {
+    std::vector<FuncWrap> vec = m->model->forward(input, output, batch, seq_len, slot);
+    DynamicNvInitParam dp;
+    dp.stream = stream;
+    int n = 0;
+    for (auto& f : vec) {
+      const int rc = f.callback(dp);
+      if (rc != LIGER_OK) return rc;
+      ++n;
+    }
+    return n;
+  } catch (const std::exception& e) {
+    return liger::set_error(LIGER_ERR_INVALID, "model_forward: %s", e.what());
+  }
+}
+
+extern "C" int liger_model_forward_host(liger_model* m, const void* host_input, void* host_output, int batch, int seq_len,
+                                        int slot, void* stream) {
+  if (!m || !host_input || !host_output) return liger::set_error(LIGER_ERR_INVALID, "model_forward_host: null argument");
+  if (batch < 1 || seq_len < 1 || (size_t)batch * seq_len > m->model->tokens_max())
+    return liger::set_error(LIGER_ERR_INVALID, "model_forward_host: batch/seq outside the configured maximum");
+  const size_t bytes = (size_t)batch * seq_len * m->model->H * 2;
+  cudaStream_t s = (cudaStream_t)stream;
+  LIGER_CUDA_TRY(cudaMemcpyAsync(m->io_in, host_input, bytes, cudaMemcpyHostToDevice, s));
+  const int n = liger_model_forward(m, m->io_in, m->io_out, batch, seq_len, slot, stream);
+  if (n < 0) return n;
+  LIGER_CUDA_TRY(cudaMemcpyAsync(host_output, m->io_out, bytes, cudaMemcpyDeviceToHost, s));
+  return n;
+}
+
+extern "C" int liger_model_set_mask(liger_model* m, const void* mask) {
+  if (!m) return liger::set_error(LIGER_ERR_INVALID, "model_set_mask: null model");
+  m->model->set_mask((const half_t*)mask);
+  return LIGER_OK;
+}
+
+extern "C" int liger_serve(liger_model* m, int mode, liger_bcast_int_fn bcast, liger_barrier_fn barrier, void* ctx,
+                           const char* profile_dir, int print, liger_serving_metrics* metrics) {
+  if (!m) return liger::set_error(LIGER_ERR_INVALID, "serve: null model");
+  if (m->sp.world_size > 1 && (!bcast || !barrier))
+    return liger::set_error(LIGER_ERR_INVALID, "serve: world_size > 1 needs the broadcast and barrier callbacks");
+  try {
+    CudaRuntime rt;
+    CallbackCoordinator coord(m->sp.world_rank, m->sp.world_size, bcast, barrier, ctx);
+    const std::string dir = (profile_dir && *profile_dir) ? std::string(profile_dir) + "/" : std::string("./");
+    const std::string main_f = dir + profile_file_name("Main", m->bp, m->sp.world_size).substr(2);
+    const std::string sub_f = dir + profile_file_name("Sub", m->bp, m->sp.world_size).substr(2);
+    const size_t n = m->model->tokens_max() * m->model->H;
+    host_check(liger_fill_normal(m->io_in, (int)m->model->tokens_max(), m->model->H, m->model->H, 0, 0, m->model->H,
+                                 m->bp.seed, 0x10000u, 0.0f, 1.0f, 0, nullptr), "fill input");
+    (void)n;
+    Scheduler<Bert_Model> scheduler(m->model, m->bp, m->sp, m->io_in, m->io_out, &rt, &coord);
+    if (mode == LIGER_MODE_PROFILE) {
+      const int step = m->bp.seq_round > 0 ? m->bp.seq_round : 1;
+      const int wb = std::min(2, m->bp.max_batch_size);
+      int wsq = std::min(64, m->bp.max_seq_len);
+      wsq = std::max(step, wsq / step * step);
+      if (wb != m->bp.max_batch_size) scheduler.profile(wb, wb + 1, wsq, wsq + 1, main_f, sub_f, 1);
+      scheduler.profile(m->bp.max_batch_size, m->bp.max_batch_size + 1, 1, m->bp.max_seq_len + 1, main_f, sub_f, step);
+      return LIGER_OK;
+    }
+    scheduler.load_profiles(main_f, sub_f);
+    scheduler.serving();
+    coord.barrier();
+    if (mode == LIGER_MODE_SCHEDULE) scheduler.run_stream_sync();
+    else if (mode == LIGER_MODE_NO_SCHEDULE) scheduler.run_sequential();
+    else return liger::set_error(LIGER_ERR_INVALID, "serve: unknown mode %d", mode);
+    scheduler.run_stop();
+    ServingMetrics sm = scheduler.output_recording(print != 0);
+    fill_metrics(metrics, sm, scheduler.segments, scheduler.secondary_launches, scheduler.decompositions);
+    unsigned int st[4];
+    if (liger_device_status(st) != 0)
+      return liger::set_error(LIGER_ERR_DEVICE, "serve: device status %u at %#x (%u, %u)", st[0], st[1], st[2], st[3]);
+    return sm.launch_errors ? liger::set_error(LIGER_ERR_CUDA, "serve: %d kernel launches failed: %s", sm.launch_errors,
+                                               liger_last_error())
+                            : LIGER_OK;
+  } catch (const std::exception& e) {
+    return liger::set_error(LIGER_ERR_INVALID, "serve: %s", e.what());
+  }
+}
+
+// ---- the scheduler on a simulated device --------------------------------------------------------------
+namespace {
+
+struct SimModel {
+  SimRuntime* rt;
+  BertInitParam bp;
+  std::vector<liger_sim_kernel> kernels;
+  double slice_overhead_ms;
+  int next_request = 0;
+
+  float scaled(float base, int bs, int sq) const {
+    return base * (float)((double)bs * sq / ((double)bp.max_batch_size * bp.max_seq_len));
+  }
+  std::vector<FuncWrap> forward(const void*, void*, int bs, int sq, int /*slot*/) {
+    std::vector<FuncWrap> vec;
+    const int req = next_request++;
+    for (int l = 0; l < bp.layer_num; ++l)
+      for (size_t k = 0; k < kernels.size(); ++k) {
+        const float dur = scaled(kernels[k].duration_ms, bs, sq);
+        const int tag = (req << 16) | (l << 8) | (int)k;
+        SimRuntime* r = rt;
+        FuncWrap f((int)k, dur, (layer_type)kernels[k].type,
+                   [r, dur, tag](const DynamicNvInitParam& d) { r->launch(d.stream, dur, tag); return LIGER_OK; });
+        if (kernels[k].type == GEMM || kernels[k].type == COMMUNICATION) {
+          const double ovh = slice_overhead_ms;
+          f.slicer = [r, dur, tag, ovh](int ub, int ue, int factor) {
+            const float sd = (float)(ovh + (double)dur * (ue - ub) / factor);
+            const int stag = tag | (ub << 24) | (ue << 28);
+            return [r, sd, stag](const DynamicNvInitParam& d) { r->launch(d.stream, sd, stag); return LIGER_OK; };
+          };
+        }
+        vec.push_back(f);
+      }
+    return vec;
+  }
+};
+
+}  // namespace
+
+extern "C" int liger_sim_serve(const liger_model_config* cfg, const liger_sim_kernel* layer_kernels, int kernels_per_layer,
+                               int mode, double overlap_rate, double slice_overhead_ms, liger_sim_launch* log,
+                               int log_capacity, int* log_count, liger_serving_metrics* metrics) {
+  int rc = validate(cfg);
+  if (rc != LIGER_OK) return rc;
+  if (!layer_kernels || kernels_per_layer < 1 || kernels_per_layer > 255 || cfg->factor > 15 || cfg->layer_num > 255)
+    return liger::set_error(LIGER_ERR_INVALID, "sim_serve: bad kernel list (<= 255 kernels, factor <= 15)");
+  try {
+    SimRuntime rt;
+    rt.overlap_rate = overlap_rate;
+    Coordinator coord;
+    SimModel model{&rt, to_params(*cfg), std::vector<liger_sim_kernel>(layer_kernels, layer_kernels + kernels_per_layer),
+                   slice_overhead_ms};
+    StaticNvInitParam sp(0, 1, nullptr, 1);
+    Scheduler<SimModel> scheduler(&model, model.bp, sp, nullptr, nullptr, &rt, &coord);
+    // the cost model: isolated durations, as a profile run on this simulated device would measure
+    const std::vector<Request> reqs = make_requests(model.bp, model.bp.num_requests, model.bp.seed);
+    for (const Request& r : reqs)
+      for (int k = 0; k < kernels_per_layer; ++k) {
+        const float dur = model.scaled(layer_kernels[k].duration_ms, r.batch_size, r.seq_len);
+        scheduler.profiling_res_dict[{k, r.batch_size, r.seq_len}] = dur;
+        if (layer_kernels[k].type != COMPUTATION) {
+          std::vector<float> v;
+          for (int n = 1; n < cfg->factor; ++n) v.push_back((float)(slice_overhead_ms + (double)dur * n / cfg->factor));
+          scheduler.profiling_decompse_res_dict[{k, r.batch_size, r.seq_len}] = v;
+        }
+      }
+    scheduler.set_requests(reqs);
+    if (mode == LIGER_MODE_SCHEDULE) scheduler.run_stream_sync();
+    else if (mode == LIGER_MODE_NO_SCHEDULE) scheduler.run_sequential();
+    else return liger::set_error(LIGER_ERR_INVALID, "sim_serve: unknown mode %d", mode);
+    ServingMetrics sm = scheduler.output_recording(false);
+    fill_metrics(metrics, sm, scheduler.segments, scheduler.secondary_launches, scheduler.decompositions);
+    int n = 0;
+    for (const auto& r : rt.log) {
+      if (log && n < log_capacity) {
+        liger_sim_launch& o = log[n];
+        o.request = (r.tag >> 16) & 0xff; o.layer = (r.tag >> 8) & 0xff; o.name = r.tag & 0xff; o.stream = r.stream;
+        o.units_begin = (r.tag >> 24) & 0xf; o.units_end = (r.tag >> 28) & 0xf;
+        o.duration_ms = r.duration; o.t_start_ms = r.t_start; o.t_end_ms = r.t_end;
+      }
+      ++n;
+    }
+    if (log_count) *log_count = n;
+    return LIGER_OK;
+  } catch (const std::exception& e) {
+    return liger::set_error(LIGER_ERR_INVALID, "sim_serve: %s", e.what());
+  }
+}

@@ -104,7 +104,9 @@ enum liger_epilogue {
  * the result occupies columns [n_begin/2, n_end/2) of c.
  * For LIGER_EPI_QKV_SPLIT, N = 3 * heads * head_dim, row m = b * seq_len + s, and feature
  * n = which * heads * head_dim + head * head_dim + d is stored to
- * {q,k,v}_out[which][((b * heads + head) * seq_len + s) * head_dim + d].
+ * {q,k,v}_out[which][((b * heads + head) * seq_len + s) * head_dim + d].  With kv_stride > 0 the K and V
+ * outputs are instead rows kv_pos + s of a KV cache laid out [B, heads, kv_stride, head_dim]
+ * (prefill fills the cache from position kv_pos = 0, a decode step appends at kv_pos = kv_len).
  */
 typedef struct liger_gemm_args {
   const void* a;        /* [M, K] fp16 */
@@ -120,6 +122,7 @@ typedef struct liger_gemm_args {
   int n_begin, n_end;
   int epilogue;
   int seq_len, heads, head_dim; /* LIGER_EPI_QKV_SPLIT only */
+  int kv_stride, kv_pos;        /* LIGER_EPI_QKV_SPLIT only: see above; 0, 0 for plain [B, h, S, D] outputs */
 } liger_gemm_args;
 
 LIGER_API int liger_gemm_fp16(const liger_gemm_args* args, void* stream);
@@ -232,7 +235,8 @@ LIGER_API int liger_comm_world_size(liger_comm* comm);
  * Every rank holds its partial [M, N] fp16 at byte offset partial_off of its segment.  Rank r owns
  * rows [r*ceil(M/ws), (r+1)*ceil(M/ws)).  For each owned row in [row_begin, row_end):
  *     t = sum_p partial_p[row]            fp32; order: own partial first, then increasing rank, cyclic
- *     if hidden:  t += hidden[row] + bias ; hidden[row] = fp16(t)   (residual stream, local, owner rows)
+ *     if hidden:  t += residual_in[row] + bias ; hidden[row] = fp16(t)   (residual stream, local, owner
+ *                 rows; residual_in may equal hidden, or be NULL to mean hidden)
  *     if gamma:   o = LayerNorm(fp16(t)) * gamma + beta   else   o = fp16(t)
  *     store o to row `row` of the [M, N] tensor at byte offset out_off of EVERY rank's segment
  * preceded and followed by a cross-rank barrier on flag set `channel`, so that a kernel launched
@@ -242,9 +246,117 @@ LIGER_API int liger_comm_world_size(liger_comm* comm);
  * N % 8 == 0, N <= 16384.  row_begin / row_end allow the collective to be issued in slices
  * (decompose_comm_callback, src/utils.h:262-281).
  */
-LIGER_API int liger_allreduce_fused(liger_comm* comm, int channel, size_t partial_off, size_t out_off, void* hidden,
-                                    const void* bias, const void* gamma, const void* beta, int m, int n, int row_begin,
-                                    int row_end, int one_shot, void* stream);
+LIGER_API int liger_allreduce_fused(liger_comm* comm, int channel, size_t partial_off, size_t out_off,
+                                    const void* residual_in, void* hidden, const void* bias, const void* gamma,
+                                    const void* beta, int m, int n, int row_begin, int row_end, int one_shot,
+                                    void* stream);
+
+/* ------------------------------------------------------------------------------------------ */
+/* The layer stack and the serving entry points                                               */
+/* ------------------------------------------------------------------------------------------ */
+
+/*
+ * Configuration: the reference's eight integers (src/main.cu:14-21; BertInitParam,
+ * src/context.h:58-85) followed by the settings the reference hard-codes or lacks.
+ * liger_model_config_init() fills in the reference's defaults.
+ */
+typedef struct liger_model_config {
+  int max_batch_size, max_seq_len, head_num, size_per_head, layer_num, kernel_num, factor;
+  int rq_interval;   /* microseconds between requests = 1e6 / arrival rate (src/main.cu:33) */
+  int graph;         /* 0: reference graph (post-LayerNorm, no residual); 1: pre-LayerNorm + residual */
+  int act;           /* 0: bias + GELU; 1: GeGLU */
+  int ffn_inner;     /* 0 -> 4 * hidden */
+  int causal;        /* 1: causal mask by construction; 0: mask tensor (all ones unless set) */
+  uint32_t seed;
+  int num_requests;  /* 150 (src/schedule.h:295) */
+  int ignore_num;    /* 20 (src/schedule.h:327) */
+  int schedule_deep; /* 6 (src/schedule.h:30) */
+  float contention;  /* 0.8 (src/schedule.h:249) */
+  int poisson;       /* 0: fixed-interval arrivals, 1: exponential gaps */
+  int min_seq_len;   /* 16 */
+  int seq_round;     /* request lengths are rounded up to a multiple of this (profile bucket) */
+  int workspace_slots;
+  int kv_capacity;
+} liger_model_config;
+
+LIGER_API void liger_model_config_init(liger_model_config* cfg);
+
+typedef struct liger_model liger_model;
+
+/* Bytes of communicator data region a model with this configuration needs (0 for world_size 1). */
+LIGER_API size_t liger_model_comm_bytes(const liger_model_config* cfg, int world_size);
+
+/*
+ * Builds the layer stack on the current device: seeded weights (each rank keeps its tensor-parallel
+ * shard of the full-shape tensors), per-request workspaces, and the function-assembly machinery.
+ * Replaces `new Bert_Model<T>(BertParams, SParams, k, n, workspace)` (src/layer/bert.h:88-102,
+ * src/test_schedule.h:35).  comm may be NULL when world_size == 1.
+ */
+LIGER_API int liger_model_create(liger_model** out, const liger_model_config* cfg, int rank, int world_size,
+                                 liger_comm* comm);
+LIGER_API int liger_model_destroy(liger_model* model);
+
+/*
+ * One forward pass: assembles the kernel vector of a (batch, seq_len) request
+ * (Bert_Model::forward, src/layer/bert.h:104-115) and launches every kernel in order on `stream`
+ * (what Scheduler::run_sequential does for one request, src/schedule.h:204-219).  input / output are
+ * [batch*seq_len, hidden] fp16 in device memory.  slot selects the activation workspace (-1: round
+ * robin).  Returns the number of kernels launched, or a negative error.
+ */
+LIGER_API int liger_model_forward(liger_model* model, const void* input, void* output, int batch, int seq_len, int slot,
+                                  void* stream);
+/* Same with HOST buffers: copies the input to the device, runs the pass, copies the result back,
+ * all on `stream`; returns after enqueueing (synchronise the stream before reading host_output). */
+LIGER_API int liger_model_forward_host(liger_model* model, const void* host_input, void* host_output, int batch,
+                                       int seq_len, int slot, void* stream);
+/* Attention mask [max_batch, S, S] fp16 of 0/1 used when cfg.causal == 0 (NULL: all ones). */
+LIGER_API int liger_model_set_mask(liger_model* model, const void* mask);
+
+/* Cross-rank callbacks the serving loop needs: broadcast one int from rank 0, and a barrier.  Both
+ * may be NULL when world_size == 1. */
+typedef int (*liger_bcast_int_fn)(void* ctx, int* value);
+typedef int (*liger_barrier_fn)(void* ctx);
+
+typedef struct liger_serving_metrics {
+  int records;                  /* requests counted (after dropping the first ignore_num) */
+  int launch_errors;
+  double total_duration_ms;     /* the reference's Total_Duration */
+  double throughput_samples_s;  /* the reference's Throughput */
+  double average_latency_ms;    /* the reference's Average Latency */
+  double tokens_per_s, p50_latency_ms, p99_latency_ms, mean_gpu_ms;
+  long long tokens;
+  long long segments, secondary_launches, decompositions;
+} liger_serving_metrics;
+
+#define LIGER_MODE_PROFILE 0     /* test_profile     (src/test_schedule.h:80-104) */
+#define LIGER_MODE_SCHEDULE 1    /* test_schedule    (src/test_schedule.h:19-47): Liger's interleaved schedule */
+#define LIGER_MODE_NO_SCHEDULE 2 /* test_no_schedule (src/test_schedule.h:50-78): unscheduled baseline */
+
+/*
+ * Runs one of the three entry points on an existing model.  Profile files are read / written in
+ * `profile_dir` under the reference's names Main_<ws>_<size_per_head>_<head_num>_<max_batch>_<max_seq>.json
+ * and Sub_... (rank 0 writes, every rank reads).  metrics may be NULL (and is unused for PROFILE).
+ */
+LIGER_API int liger_serve(liger_model* model, int mode, liger_bcast_int_fn bcast, liger_barrier_fn barrier, void* ctx,
+                          const char* profile_dir, int print, liger_serving_metrics* metrics);
+
+/*
+ * The scheduling logic on a simulated device (no GPU): a layer is given as kernels_per_layer
+ * (type, milliseconds at max_batch*max_seq tokens) pairs, durations scale with the token count, a
+ * GEMM slice of n/factor costs slice_overhead_ms + n/factor of the whole, and two kernels running
+ * at once each progress at overlap_rate.  Runs `mode` (SCHEDULE or NO_SCHEDULE) over the seeded
+ * request schedule and reports every launch.  Used by the CPU tests of the scheduler.
+ */
+typedef struct liger_sim_kernel { int type; float duration_ms; } liger_sim_kernel; /* type: 0 COMM, 1 COMP, 2 GEMM */
+typedef struct liger_sim_launch {
+  int request, layer, name, stream, units_begin, units_end;
+  float duration_ms;
+  double t_start_ms, t_end_ms;
+} liger_sim_launch;
+LIGER_API int liger_sim_serve(const liger_model_config* cfg, const liger_sim_kernel* layer_kernels,
+                              int kernels_per_layer, int mode, double overlap_rate, double slice_overhead_ms,
+                              liger_sim_launch* log, int log_capacity, int* log_count,
+                              liger_serving_metrics* metrics);
 
 #ifdef __cplusplus
 }

@@ -49,7 +49,7 @@ def _worker(rank, world, port, results):
         for rep in range(2):   # second call re-uses the flags with new epochs
             if use_h:
                 dev_fill(liger, m, n, 0, 510, out=hidden)
-            liger.check(lib.liger_allreduce_fused(comm.handle, rep % 2, 0, out_off, ptr(hidden) if use_h else None,
+            liger.check(lib.liger_allreduce_fused(comm.handle, rep % 2, 0, out_off, None, ptr(hidden) if use_h else None,
                                                   ptr(bias) if use_h else None, ptr(g) if use_ln else None,
                                                   ptr(b) if use_ln else None, m, n, 0, m, 1 if mode == "one_shot" else 0,
                                                   stream_ptr()))
