@@ -21,6 +21,15 @@ struct liger_model {
   half_t* io_in = nullptr;   // device staging for the host-buffer entry point
   half_t* io_out = nullptr;
   int device = 0;
+  bool timing = false;
+  std::vector<cudaEvent_t> ev_pool;                      // reusable events
+  std::vector<std::pair<int, std::pair<cudaEvent_t, cudaEvent_t>>> ev_rec;  // (name, (before, after))
+  cudaEvent_t get_event() {
+    if (!ev_pool.empty()) { cudaEvent_t e = ev_pool.back(); ev_pool.pop_back(); return e; }
+    cudaEvent_t e = nullptr;
+    cudaEventCreate(&e);
+    return e;
+  }
 };
 
 namespace {
@@ -128,7 +137,10 @@ extern "C" int liger_model_forward(liger_model* m, const void* input, void* outp
     dp.stream = stream;
     int n = 0;
     for (auto& f : vec) {
+      cudaEvent_t e0 = nullptr, e1 = nullptr;
+      if (m->timing) { e0 = m->get_event(); e1 = m->get_event(); cudaEventRecord(e0, (cudaStream_t)stream); }
       const int rc = f.callback(dp);
+      if (m->timing) { cudaEventRecord(e1, (cudaStream_t)stream); m->ev_rec.push_back({f.name, {e0, e1}}); }
       if (rc != LIGER_OK) return rc;
       ++n;
     }
@@ -150,6 +162,50 @@ extern "C" int liger_model_forward_host(liger_model* m, const void* host_input, 
   if (n < 0) return n;
   LIGER_CUDA_TRY(cudaMemcpyAsync(host_output, m->io_out, bytes, cudaMemcpyDeviceToHost, s));
   return n;
+}
+
+extern "C" int liger_model_set_kernel_timing(liger_model* m, int enable) {
+  if (!m) return liger::set_error(LIGER_ERR_INVALID, "model_set_kernel_timing: null model");
+  m->timing = enable != 0;
+  return LIGER_OK;
+}
+
+extern "C" int liger_model_kernel_times(liger_model* m, double ms[9], long long launches[9]) {
+  if (!m || !ms || !launches) return liger::set_error(LIGER_ERR_INVALID, "model_kernel_times: null argument");
+  for (auto& r : m->ev_rec) {
+    float t = 0.0f;
+    LIGER_CUDA_TRY(cudaEventSynchronize(r.second.second));
+    LIGER_CUDA_TRY(cudaEventElapsedTime(&t, r.second.first, r.second.second));
+    if (r.first >= 0 && r.first < 9) { ms[r.first] += t; launches[r.first] += 1; }
+    m->ev_pool.push_back(r.second.first);
+    m->ev_pool.push_back(r.second.second);
+  }
+  m->ev_rec.clear();
+  return LIGER_OK;
+}
+
+extern "C" int liger_model_kernel_work(liger_model* m, int name, int batch, int seq_len, double* flops, double* bytes) {
+  if (!m || !flops || !bytes) return liger::set_error(LIGER_ERR_INVALID, "model_kernel_work: null argument");
+  const Bert_Model& b = *m->model;
+  const double M = (double)batch * seq_len, H = b.H, Hl = b.Hl, Fl = b.Fl, ws = m->sp.world_size;
+  const double up = m->bp.act == ACT_GEGLU ? 2.0 * Fl : Fl;
+  const bool preln = m->bp.graph == GRAPH_PRELN;
+  double f = 0.0, by = 0.0;
+  switch (name) {
+    case 0: f = 2.0 * M * H * 3.0 * Hl; by = 2.0 * (M * H + 3.0 * Hl * H + 3.0 * M * Hl); break;
+    case 1: f = 4.0 * (double)batch * b.heads_local * (double)seq_len * seq_len * b.D * (m->bp.causal ? 0.5 : 1.0);
+            by = 2.0 * 4.0 * M * Hl; break;
+    case 2: f = 2.0 * M * Hl * H; by = 2.0 * (M * Hl + H * Hl + M * H * (ws == 1 && preln ? 2.0 : 1.0)); break;
+    case 3: case 6: by = ws > 1 ? 2.0 * M * H * (1.0 + (preln ? 2.0 / ws : 0.0) + 1.0) : 2.0 * 2.0 * M * H; break;
+    case 4: f = 2.0 * M * H * up; by = 2.0 * (M * H + up * H + M * Fl); break;
+    case 5: f = 2.0 * M * Fl * H; by = 2.0 * (M * Fl + H * Fl + M * H * (ws == 1 && preln ? 2.0 : 1.0)); break;
+    case 7: by = preln ? 2.0 * 2.0 * M * H : 0.0; break;
+    case 8: by = ws > 1 ? 2.0 * 2.0 * M * H : 0.0; break;
+    default: return liger::set_error(LIGER_ERR_INVALID, "model_kernel_work: kernel name %d", name);
+  }
+  *flops = f;
+  *bytes = by;
+  return LIGER_OK;
 }
 
 extern "C" int liger_model_set_mask(liger_model* m, const void* mask) {

@@ -309,6 +309,20 @@ LIGER_API int liger_model_forward(liger_model* model, const void* input, void* o
  * all on `stream`; returns after enqueueing (synchronise the stream before reading host_output). */
 LIGER_API int liger_model_forward_host(liger_model* model, const void* host_input, void* host_output, int batch,
                                        int seq_len, int slot, void* stream);
+/*
+ * Per-kernel timing of liger_model_forward[_host]: when enabled, the pass records a CUDA event on
+ * `stream` before and after every kernel it launches.  liger_model_kernel_times() waits for the
+ * recorded events, adds the elapsed milliseconds and launch counts per kernel name (0..8, see
+ * liger_model_forward) into ms[9] / launches[9], and clears the record.  This is the measurement
+ * Scheduler::profile makes one kernel at a time (src/schedule.h:93-112), taken in situ.
+ */
+LIGER_API int liger_model_set_kernel_timing(liger_model* model, int enable);
+LIGER_API int liger_model_kernel_times(liger_model* model, double ms[9], long long launches[9]);
+/* Algorithmic FLOPs of kernel `name` (GEMMs: 2*M*N*K of this rank's shard; attention: QK^T + PV,
+ * halved when causal) and the bytes it must move (operands + results once), for one request of
+ * (batch, seq_len); 0 for names that do not exist in this configuration. */
+LIGER_API int liger_model_kernel_work(liger_model* model, int name, int batch, int seq_len, double* flops,
+                                      double* bytes);
 /* Attention mask [max_batch, S, S] fp16 of 0/1 used when cfg.causal == 0 (NULL: all ones). */
 LIGER_API int liger_model_set_mask(liger_model* model, const void* mask);
 

@@ -41,6 +41,7 @@ def lib():
             build()
         _lib = C.CDLL(LIB)
         _lib.lo_num_threads.restype = C.c_int
+        _lib.lo_fill_seconds.restype = C.c_double
     return _lib
 
 
@@ -50,6 +51,11 @@ def _p(a):
 
 def _f32(a):
     return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def fill_seconds(reset=False):
+    """Seconds spent generating seeded tensors since the last reset."""
+    return lib().lo_fill_seconds(int(reset))
 
 
 def num_threads():

@@ -44,6 +44,22 @@ LO_API int lo_num_threads(void) {
 #endif
 }
 
+/* Seconds spent generating seeded tensors since the last reset: lets a caller that times the stack
+ * separate the arithmetic from the cost of materialising the weights. */
+static double g_fill_seconds = 0.0;
+static double now_seconds(void) {
+#ifdef _OPENMP
+  return omp_get_wtime();
+#else
+  return 0.0;
+#endif
+}
+LO_API double lo_fill_seconds(int reset) {
+  double v = g_fill_seconds;
+  if (reset) g_fill_seconds = 0.0;
+  return v;
+}
+
 /* dst[i] = value of element (idx0 + i) of seeded tensor `tensor_id`, as fp16 bits */
 LO_API void lo_fill_normal_f16(uint16_t* dst, uint64_t n, uint32_t seed, uint32_t tensor_id, uint64_t idx0,
                                float mean, float std) {
@@ -54,19 +70,23 @@ LO_API void lo_fill_normal_f16(uint16_t* dst, uint64_t n, uint32_t seed, uint32_
 /* the same values widened to float */
 LO_API void lo_fill_normal_f32(float* dst, uint64_t n, uint32_t seed, uint32_t tensor_id, uint64_t idx0, float mean,
                                float std) {
+  const double t0 = now_seconds();
 #pragma omp parallel for schedule(static)
   for (int64_t i = 0; i < (int64_t)n; ++i)
     dst[i] = lg_half_bits_to_float(lg_normal_half_bits(seed, tensor_id, idx0 + (uint64_t)i, mean, std));
+  g_fill_seconds += now_seconds() - t0;
 }
 
 /* a [rows x cols] window (row0.., col0..) of a seeded logical matrix with `ld` columns */
 LO_API void lo_fill_normal_window_f32(float* dst, int rows, int cols, int row0, int col0, int ld, uint32_t seed,
                                       uint32_t tensor_id, float mean, float std) {
+  const double t0 = now_seconds();
 #pragma omp parallel for schedule(static)
   for (int r = 0; r < rows; ++r)
     for (int c = 0; c < cols; ++c)
       dst[(size_t)r * cols + c] = lg_half_bits_to_float(
           lg_normal_half_bits(seed, tensor_id, (uint64_t)(row0 + r) * (uint64_t)ld + (uint64_t)(col0 + c), mean, std));
+  g_fill_seconds += now_seconds() - t0;
 }
 
 LO_API void lo_half_to_float(const uint16_t* src, float* dst, uint64_t n) {
@@ -88,17 +108,19 @@ LO_API void lo_round_fp16(float* x, uint64_t n) {
 /* Y[M,N] = X[M,K] * W[K,N]; ldx / ldw / ldy are row strides so that a rank's slice of the      */
 /* full weight can be addressed in place.                                                     */
 /* ------------------------------------------------------------------------------------------ */
-static void gemm_block(const float* X, int ldx, const float* W, int ldw, float* Y, int ldy, int i0, int i1, int N,
-                       int K) {
+/* one task: rows [i0,i1) x columns [j0,j1), full K, accumulating into Y in k-blocks of 256 so that the
+ * W sub-block (256 x 64 floats) and the X sub-block stay in cache */
+static void gemm_task(const float* X, int ldx, const float* W, int ldw, float* Y, int ldy, int i0, int i1, int j0, int j1,
+                      int K) {
   const int KB = 256;
-  for (int i = i0; i < i1; ++i) memset(Y + (size_t)i * ldy, 0, sizeof(float) * (size_t)N);
+  for (int i = i0; i < i1; ++i) memset(Y + (size_t)i * ldy + j0, 0, sizeof(float) * (size_t)(j1 - j0));
   for (int kb = 0; kb < K; kb += KB) {
     const int ke = kb + KB < K ? kb + KB : K;
     int i = i0;
 #if defined(__AVX2__) && defined(__FMA__)
     for (; i + 4 <= i1; i += 4) {
-      int j = 0;
-      for (; j + 16 <= N; j += 16) {
+      int j = j0;
+      for (; j + 16 <= j1; j += 16) {
         float* y0 = Y + (size_t)(i + 0) * ldy + j;
         float* y1 = Y + (size_t)(i + 1) * ldy + j;
         float* y2 = Y + (size_t)(i + 2) * ldy + j;
@@ -124,7 +146,7 @@ static void gemm_block(const float* X, int ldx, const float* W, int ldw, float* 
         _mm256_storeu_ps(y2, a20); _mm256_storeu_ps(y2 + 8, a21);
         _mm256_storeu_ps(y3, a30); _mm256_storeu_ps(y3 + 8, a31);
       }
-      for (; j < N; ++j)
+      for (; j < j1; ++j)
         for (int r = 0; r < 4; ++r) {
           float acc = Y[(size_t)(i + r) * ldy + j];
           for (int k = kb; k < ke; ++k) acc += X[(size_t)(i + r) * ldx + k] * W[(size_t)k * ldw + j];
@@ -137,20 +159,22 @@ static void gemm_block(const float* X, int ldx, const float* W, int ldw, float* 
       for (int k = kb; k < ke; ++k) {
         const float x = X[(size_t)i * ldx + k];
         const float* w = W + (size_t)k * ldw;
-        for (int j = 0; j < N; ++j) y[j] += x * w[j];
+        for (int j = j0; j < j1; ++j) y[j] += x * w[j];
       }
     }
   }
 }
 
 LO_API void lo_linear(const float* X, int ldx, const float* W, int ldw, float* Y, int ldy, int M, int N, int K) {
-  const int RB = 8;
-  const int nblk = (M + RB - 1) / RB;
-#pragma omp parallel for schedule(dynamic, 1)
-  for (int b = 0; b < nblk; ++b) {
-    int i0 = b * RB, i1 = i0 + RB < M ? i0 + RB : M;
-    gemm_block(X, ldx, W, ldw, Y, ldy, i0, i1, N, K);
-  }
+  const int RB = 128, CB = 64;
+  const int nrb = (M + RB - 1) / RB, ncb = (N + CB - 1) / CB;
+#pragma omp parallel for collapse(2) schedule(dynamic, 1)
+  for (int rb = 0; rb < nrb; ++rb)
+    for (int cb = 0; cb < ncb; ++cb) {
+      const int i0 = rb * RB, i1 = i0 + RB < M ? i0 + RB : M;
+      const int j0 = cb * CB, j1 = j0 + CB < N ? j0 + CB : N;
+      gemm_task(X, ldx, W, ldw, Y, ldy, i0, i1, j0, j1, K);
+    }
 }
 
 /* ------------------------------------------------------------------------------------------ */

@@ -1,0 +1,147 @@
+"""Whole-stack parity: the function-assembled layer stack (liger_model_forward) against the fp32 CPU
+oracle on the same seeded weights and inputs.  Bound: max |got - want| / max |want| <= 1e-2 against
+the pure-fp32 oracle (the GPU path stores fp16 between kernels and accumulates in fp32; with
+world_size > 1 the partial sums are rounded to fp16 before the fp32 reduction, whose order starts
+at the owning rank instead of rank 0)."""
+import ctypes as C
+import os
+import sys
+
+import numpy as np
+import pytest
+
+from helpers import assert_close, dev_fill, max_rel_err, ptr, stream_ptr, to_np
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+CASES = {
+    # the reference graph: post-LayerNorm, no residual, GELU 4H, mask tensor of ones (src/layer/bert.h:59-79)
+    "ref_gelu": dict(head_num=4, size_per_head=64, layer_num=2, graph=0, act=0, ffn_inner=0, causal=0, B=2, S=64),
+    # BASELINE config 1: 2 layers, hidden 1024, 16 x 64, FFN 4096 GELU, pre-LN, causal, batch 4 x seq 128
+    "tiny_preln": dict(head_num=16, size_per_head=64, layer_num=2, graph=1, act=0, ffn_inner=4096, causal=1, B=4, S=128),
+    # gated FFN, head_dim 128, ragged sequence length
+    "preln_geglu": dict(head_num=4, size_per_head=128, layer_num=3, graph=1, act=1, ffn_inner=1024, causal=1, B=3, S=72),
+    "ref_geglu_causal": dict(head_num=8, size_per_head=64, layer_num=1, graph=0, act=1, ffn_inner=2048, causal=1, B=1, S=200),
+}
+
+
+def make_cfg(liger, case, slots=2):
+    c = CASES[case]
+    return liger.default_config(max_batch_size=c["B"], max_seq_len=c["S"], head_num=c["head_num"],
+                                size_per_head=c["size_per_head"], layer_num=c["layer_num"], graph=c["graph"], act=c["act"],
+                                ffn_inner=c["ffn_inner"], causal=c["causal"], seed=0, workspace_slots=slots,
+                                schedule_deep=1)
+
+
+def oracle_out(oracle, case, tp, round16):
+    c = CASES[case]
+    H = c["head_num"] * c["size_per_head"]
+    cfg = oracle.Config(hidden=H, heads=c["head_num"], head_dim=c["size_per_head"], ffn_inner=c["ffn_inner"] or 4 * H,
+                        layers=c["layer_num"], tp=tp, graph=c["graph"], act=c["act"], causal=c["causal"], round16=round16,
+                        seed=0)
+    M = c["B"] * c["S"]
+    x = oracle.fill_normal(M * H, 0, oracle.INPUT).reshape(M, H)
+    return oracle.stack_forward(cfg, x, c["B"], c["S"])
+
+
+@pytest.mark.parametrize("case", list(CASES))
+def test_stack_forward_single_gpu(gpu, liger, oracle, case):
+    import torch
+    c = CASES[case]
+    H = c["head_num"] * c["size_per_head"]
+    M = c["B"] * c["S"]
+    cfg = make_cfg(liger, case)
+    model = C.c_void_p()
+    liger.check(gpu.liger_model_create(C.byref(model), C.byref(cfg), 0, 1, None))
+    x = dev_fill(liger, M, H, 0, oracle.INPUT)
+    out = torch.zeros((M, H), dtype=torch.float16, device="cuda")
+    n = liger.check(gpu.liger_model_forward(model, ptr(x), ptr(out), c["B"], c["S"], 0, stream_ptr()))
+    torch.cuda.synchronize()
+    st = (C.c_uint * 4)()
+    assert gpu.liger_device_status(C.byref(st)) == 0, list(st)
+    assert n == 7 * c["layer_num"]   # pre-LN: one LayerNorm in front, none after the last layer
+    want = oracle_out(oracle, case, 1, 0)
+    assert_close(to_np(out), want, rel=1e-2, what=case)
+    # the oracle with fp16 rounding at the same places agrees more closely
+    assert max_rel_err(to_np(out), oracle_out(oracle, case, 1, 1)) < 5e-3
+    # host-buffer entry point gives the same bits; a second slot too
+    hin = x.cpu().pin_memory()
+    hout = torch.zeros((M, H), dtype=torch.float16).pin_memory()
+    liger.check(gpu.liger_model_forward_host(model, C.c_void_p(hin.data_ptr()), C.c_void_p(hout.data_ptr()), c["B"],
+                                             c["S"], 1, stream_ptr()))
+    torch.cuda.synchronize()
+    assert torch.equal(hout, out.cpu())
+    gpu.liger_model_destroy(model)
+
+
+def test_shorter_request_than_maximum(gpu, liger, oracle):
+    """A request smaller than (max_batch, max_seq) uses the same model (ragged serving lengths)."""
+    import torch
+    case = "tiny_preln"
+    c = dict(CASES[case])
+    cfg = make_cfg(liger, case)
+    model = C.c_void_p()
+    liger.check(gpu.liger_model_create(C.byref(model), C.byref(cfg), 0, 1, None))
+    B, S, H = 2, 36, 1024
+    x = dev_fill(liger, B * S, H, 0, oracle.INPUT)
+    out = torch.zeros((B * S, H), dtype=torch.float16, device="cuda")
+    liger.check(gpu.liger_model_forward(model, ptr(x), ptr(out), B, S, -1, stream_ptr()))
+    ocfg = oracle.Config(hidden=H, heads=16, head_dim=64, ffn_inner=4096, layers=2, tp=1, graph=1, act=0, causal=1,
+                         round16=0, seed=0)
+    want = oracle.stack_forward(ocfg, to_np(x), B, S)
+    assert_close(to_np(out), want, rel=1e-2, what="short request")
+    assert gpu.liger_model_forward(model, ptr(x), ptr(out), 5, 128, 0, stream_ptr()) == -1   # batch > max
+    gpu.liger_model_destroy(model)
+
+
+def _tp_worker(rank, world, port, case, results):
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, HERE)
+    sys.path.insert(0, os.path.dirname(HERE))
+    from conftest import load_package
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    liger = load_package()
+    from liger_b200.dist import Comm
+    lib = liger.lib()
+    c = CASES[case]
+    H = c["head_num"] * c["size_per_head"]
+    M = c["B"] * c["S"]
+    cfg = make_cfg(liger, case)
+    comm = Comm(rank, world, lib.liger_model_comm_bytes(C.byref(cfg), world), channels=cfg.workspace_slots)
+    model = C.c_void_p()
+    liger.check(lib.liger_model_create(C.byref(model), C.byref(cfg), rank, world, comm.handle))
+    x = dev_fill(liger, M, H, 0, 0x10000)
+    out = torch.zeros((M, H), dtype=torch.float16, device="cuda")
+    dist.barrier()
+    for rep in range(2):
+        liger.check(lib.liger_model_forward(model, ptr(x), ptr(out), c["B"], c["S"], rep % 2, stream_ptr()))
+        torch.cuda.synchronize()
+    st = (C.c_uint * 4)()
+    assert lib.liger_device_status(C.byref(st)) == 0, list(st)
+    results[rank] = to_np(out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("case", ["tiny_preln", "ref_gelu", "preln_geglu"])
+def test_stack_forward_tensor_parallel_2(oracle, case):
+    """BASELINE config 1 is the tiny pre-LN stack at TP = 2."""
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_tp_worker, args=(2, 29541, case, results), nprocs=2, join=True)
+    want = oracle_out(oracle, case, 2, 0)
+    for r in range(2):
+        assert_close(results[r], want, rel=1e-2, what=f"{case} rank {r}")
+    assert np.array_equal(results[0], results[1])
+    # tensor parallelism does not change the result beyond rounding: TP=2 vs the TP=1 oracle
+    assert max_rel_err(results[0], oracle_out(oracle, case, 1, 0)) < 1e-2
