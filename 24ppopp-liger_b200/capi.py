@@ -75,6 +75,8 @@ SIGNATURES = {
     "liger_attention_prefill": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _F, _I, _P]),
     "liger_attention_decode_scratch_bytes": (_SZ, [_I, _I, _I, _I]),
     "liger_attention_decode": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P]),
+    "liger_attention_decode_noalloc_max_bytes": (_SZ, []),
+    "liger_attention_decode_noalloc": (_I, [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _F, _P]),
     "liger_layernorm": (_I, [_P, _P, _P, _P, _I, _I, _P]),
     "liger_add_bias_input_layernorm": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _P]),
     "liger_add_bias_gelu": (_I, [_P, _P, _I, _I, _P]),

@@ -8,6 +8,8 @@
 //
 // Decode: one query token per sequence against a KV cache, split over the KV length so that the
 // cache streams at HBM rate; a second kernel merges the split partials.
+#include <mutex>
+
 #include "runtime.h"
 
 namespace liger {
@@ -381,6 +383,84 @@ extern "C" int liger_attention_decode(const void* q, const void* k_cache, const 
     attention_decode_merge_kernel<64><<<mgrid, 64, 0, s>>>((const float*)scratch, (__half*)out, heads, ns, ldo);
   } else {
     return set_error(LIGER_ERR_UNSUPPORTED, "attention_decode: head_dim %d (64 and 128 are implemented)", head_dim);
+  }
+  return check_launch("attention_decode_merge_kernel");
+}
+
+
+// ---- decode attention without any allocation ---------------------------------------------------------
+// Split-KV partials of liger_attention_decode_noalloc live in this file-scope device array instead of
+// caller-provided scratch.  Every device that loads the library holds these 16 MiB until the process
+// exits.  All calls on a device share it.
+namespace liger {
+constexpr size_t kStaticScratchFloats = (size_t)4 << 20;  // 4 Mi floats = 16 MiB
+static __device__ __align__(256) float g_decode_scratch[kStaticScratchFloats];
+
+constexpr int kStaticMaxDevices = 64;
+static float* g_decode_scratch_addr[kStaticMaxDevices];  // device address of the array, per device
+static std::mutex g_decode_scratch_mu;
+
+// Device address of g_decode_scratch on the current device.  In host code the array's name is only a
+// handle: the address a kernel can use has to be asked for, once per device, with that device current.
+static int static_scratch_address(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kStaticMaxDevices)
+    return set_error(LIGER_ERR_CUDA, "attention_decode_noalloc: no usable CUDA device: %s", cudaGetErrorString(e));
+  std::lock_guard<std::mutex> lk(g_decode_scratch_mu);
+  if (g_decode_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_decode_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      cudaGetLastError();
+      return set_error(LIGER_ERR_CUDA, "attention_decode_noalloc: cudaGetSymbolAddress failed on device %d: %s", dev,
+                       cudaGetErrorString(e));
+    }
+    g_decode_scratch_addr[dev] = (float*)p;
+  }
+  *out = g_decode_scratch_addr[dev];
+  return LIGER_OK;
+}
+}  // namespace liger
+
+extern "C" size_t liger_attention_decode_noalloc_max_bytes(void) { return liger::kStaticScratchFloats * sizeof(float); }
+
+extern "C" int liger_attention_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, void* out, int batch,
+                                              int heads, int kv_len, int kv_stride, int head_dim, int ldo, float scale,
+                                              void* stream) {
+  if (!q || !k_cache || !v_cache || !out || batch <= 0 || heads <= 0 || kv_len <= 0 || kv_stride < kv_len)
+    return set_error(LIGER_ERR_INVALID, "attention_decode_noalloc: bad argument");
+  if (head_dim != 64 && head_dim != 128)
+    return set_error(LIGER_ERR_UNSUPPORTED, "attention_decode_noalloc: head_dim %d (64 and 128 are implemented)", head_dim);
+  if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15u)
+    return set_error(LIGER_ERR_INVALID, "attention_decode_noalloc: q / caches must be 16-byte aligned");
+  if (batch > 65535 || heads > 65535) return set_error(LIGER_ERR_UNSUPPORTED, "attention_decode_noalloc: batch, heads <= 65535");
+  const size_t need = liger_attention_decode_scratch_bytes(batch, heads, head_dim, kv_len);
+  if (need > kStaticScratchFloats * sizeof(float))
+    return set_error(LIGER_ERR_TOO_LARGE,
+                     "attention_decode_noalloc: batch %d x heads %d x kv_len %d needs %zu bytes of split-KV partials; the built-in "
+                     "buffer holds %zu (use liger_attention_decode with caller scratch)",
+                     batch, heads, kv_len, need, kStaticScratchFloats * sizeof(float));
+  float* scratch = nullptr;
+  int rc = static_scratch_address(&scratch);
+  if (rc != LIGER_OK) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int ns = decode_splits(kv_len);
+  dim3 grid(ns, heads, batch), mgrid(heads, batch);
+  // every partial that the merge kernel reads is written by the partial kernel of the same call, so
+  // nothing left over from an earlier call is ever consumed and nothing needs clearing
+  if (head_dim == 128) {
+    attention_decode_partial_kernel<128><<<grid, kDecThreads, 0, s>>>((const __half*)q, (const __half*)k_cache,
+                                                                      (const __half*)v_cache, scratch, heads, kv_len,
+                                                                      kv_stride, scale);
+    if ((rc = check_launch("attention_decode_partial_kernel")) != LIGER_OK) return rc;
+    attention_decode_merge_kernel<128><<<mgrid, 128, 0, s>>>(scratch, (__half*)out, heads, ns, ldo);
+  } else {
+    attention_decode_partial_kernel<64><<<grid, kDecThreads, 0, s>>>((const __half*)q, (const __half*)k_cache,
+                                                                     (const __half*)v_cache, scratch, heads, kv_len,
+                                                                     kv_stride, scale);
+    if ((rc = check_launch("attention_decode_partial_kernel")) != LIGER_OK) return rc;
+    attention_decode_merge_kernel<64><<<mgrid, 64, 0, s>>>(scratch, (__half*)out, heads, ns, ldo);
   }
   return check_launch("attention_decode_merge_kernel");
 }

@@ -163,6 +163,32 @@ LIGER_API int liger_attention_decode(const void* q, const void* k_cache, const v
                            int batch, int heads, int kv_len, int kv_stride, int head_dim, int ldo, float scale,
                            void* stream);
 
+/*
+ * liger_attention_decode for callers that cannot allocate device memory.  No counterpart in the
+ * reference (it has no decode path at all); it exists for hosts where cudaMalloc is off limits at
+ * the call site -- a serving loop whose memory pool is sized and frozen at start-up, a plugin that
+ * runs inside someone else's allocator, code between two points where device allocation would
+ * synchronise the device or is simply forbidden by policy.  The split-KV partials go to a 16 MiB
+ * buffer built into the library image (one per GPU that loads the library, held until the
+ * process exits) instead of caller scratch; the call itself performs no cudaMalloc / cudaFree and
+ * calls nothing that allocates.  q, k_cache, v_cache and out are still the caller's.
+ *
+ * Limits and rules:
+ *  - batch * heads * ceil(kv_len / 256) * (head_dim + 2) * 4 bytes must not exceed
+ *    liger_attention_decode_noalloc_max_bytes() (16 MiB); larger requests return
+ *    LIGER_ERR_TOO_LARGE and launch nothing (use liger_attention_decode with your own scratch).
+ *  - The first call on each device looks up the device address of the built-in buffer
+ *    (cudaGetSymbolAddress); make that first call outside any stream capture.
+ *  - All calls on a device share the one buffer and it keeps whatever the last call left there.
+ *    Each call overwrites every partial it later reads, so stale contents are never consumed, but
+ *    two calls that overlap on the GPU (different streams, no ordering between them) race on the
+ *    buffer: serialise them.
+ */
+LIGER_API size_t liger_attention_decode_noalloc_max_bytes(void);
+LIGER_API int liger_attention_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, void* out, int batch,
+                                             int heads, int kv_len, int kv_stride, int head_dim, int ldo, float scale,
+                                             void* stream);
+
 /* ------------------------------------------------------------------------------------------ */
 /* Row-wise operators                                                                         */
 /* ------------------------------------------------------------------------------------------ */
