@@ -54,6 +54,7 @@ struct liger_comm {
   bool connected = false;
   std::vector<uint32_t> epoch;   // per channel, host side
   unsigned int* done = nullptr;  // per channel CTA-completion counters (device)
+  unsigned long long* stamps = nullptr;  // per channel: 4 globaltimer stamps of the last launch + 4 running sums
 };
 
 namespace liger {
@@ -99,7 +100,7 @@ allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t out_of
                        const __half* residual_in, __half* hidden,
                        const __half* __restrict__ bias, const __half* __restrict__ gamma,
                        const __half* __restrict__ beta, int n, int row_lo, int row_hi, int one_shot, uint32_t epoch_in,
-                       uint32_t epoch_out, unsigned int* done_counter, DeviceStatus* st) {
+                       uint32_t epoch_out, unsigned int* done_counter, unsigned long long* stamps, DeviceStatus* st) {
   __shared__ float red[32];
   __shared__ int s_fail;
   __shared__ int s_last;
@@ -107,8 +108,10 @@ allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t out_of
   __syncthreads();
 
   // ---- entry barrier: every rank's partial is complete and visible ----
+  const unsigned long long t_enter = globaltimer_ns();
   if (blockIdx.x == 0) barrier_signal(c, channel, epoch_in);
   if (!barrier_wait(c, channel, epoch_in, &s_fail, st, 0x200u)) return;
+  const unsigned long long t_go = globaltimer_ns();
 
   const int nvec = n >> 3;
   for (int row = row_lo + blockIdx.x; row < row_hi; row += gridDim.x) {
@@ -118,7 +121,8 @@ allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t out_of
     for (int i = 0; i < kArMaxVec; ++i)
 #pragma unroll
       for (int j = 0; j < 8; ++j) v[i][j] = 0.0f;
-    for (int kx = 0; kx < c.ws; ++kx) {
+    const int nsum = one_shot == 2 ? 1 : c.ws;  // gather mode: only this rank's own rows are read
+    for (int kx = 0; kx < nsum; ++kx) {
       int p = c.rank + kx;
       if (p >= c.ws) p -= c.ws;
       const __half* src = reinterpret_cast<const __half*>(c.base[p] + partial_off) + roff;
@@ -216,7 +220,7 @@ allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t out_of
 #pragma unroll
           for (int j = 0; j < 4; ++j) ow[j] = pack_half2(v[i][2 * j], v[i][2 * j + 1]);
         }
-        if (one_shot) {
+        if (one_shot == 1) {
           *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(c.base[c.rank] + out_off) + roff + (size_t)idx * 8) = o;
         } else {
           for (int kx = 0; kx < c.ws; ++kx) {
@@ -238,9 +242,16 @@ allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t out_of
   }
   __syncthreads();
   if (s_last) {
+    const unsigned long long t_work = globaltimer_ns();
     __threadfence_system();
     barrier_signal(c, channel, epoch_out);
     barrier_wait(c, channel, epoch_out, &s_fail, st, 0x201u);
+    if (threadIdx.x == 0) {
+      // stamps of the last CTA to finish: wait for peers at entry / own work / wait for peers at exit
+      const unsigned long long t_exit = globaltimer_ns();
+      stamps[0] = t_enter; stamps[1] = t_go; stamps[2] = t_work; stamps[3] = t_exit;
+      stamps[4] += t_go - t_enter; stamps[5] += t_work - t_go; stamps[6] += t_exit - t_work; stamps[7] += 1ull;
+    }
   }
 }
 
@@ -263,10 +274,13 @@ extern "C" int liger_comm_create(liger_comm** out, int rank, int world_size, siz
   if (e == cudaSuccess) e = cudaMemset(c->local, 0, kFlagRegionBytes);
   if (e == cudaSuccess) e = cudaMalloc((void**)&c->done, sizeof(unsigned int) * channels);
   if (e == cudaSuccess) e = cudaMemset(c->done, 0, sizeof(unsigned int) * channels);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&c->stamps, sizeof(unsigned long long) * 8 * channels);
+  if (e == cudaSuccess) e = cudaMemset(c->stamps, 0, sizeof(unsigned long long) * 8 * channels);
   if (e == cudaSuccess) e = cudaDeviceSynchronize();
   if (e != cudaSuccess) {
     if (c->local) cudaFree(c->local);
     if (c->done) cudaFree(c->done);
+    if (c->stamps) cudaFree(c->stamps);
     delete c;
     return set_error(LIGER_ERR_CUDA, "comm_create: allocating %zu bytes failed: %s", data_bytes, cudaGetErrorString(e));
   }
@@ -341,8 +355,18 @@ extern "C" int liger_comm_destroy(liger_comm* c) {
     if (c->ipc_open[p]) cudaIpcCloseMemHandle(c->peer[p]);
   if (c->local) cudaFree(c->local);
   if (c->done) cudaFree(c->done);
+  if (c->stamps) cudaFree(c->stamps);
   delete c;
   cudaGetLastError();
+  return LIGER_OK;
+}
+
+extern "C" int liger_comm_timing(liger_comm* c, int channel, int reset, double out_us[4]) {
+  if (!c || !out_us || channel < 0 || channel >= c->channels) return set_error(LIGER_ERR_INVALID, "comm_timing: bad argument");
+  unsigned long long h[8];
+  LIGER_CUDA_TRY(cudaMemcpy(h, c->stamps + 8 * channel, sizeof(h), cudaMemcpyDeviceToHost));
+  out_us[0] = (double)h[4] * 1e-3; out_us[1] = (double)h[5] * 1e-3; out_us[2] = (double)h[6] * 1e-3; out_us[3] = (double)h[7];
+  if (reset) LIGER_CUDA_TRY(cudaMemset(c->stamps + 8 * channel, 0, sizeof(h)));
   return LIGER_OK;
 }
 
@@ -374,8 +398,9 @@ extern "C" int liger_allreduce_fused(liger_comm* c, int channel, size_t partial_
   CommDev cd;
   for (int p = 0; p < kMaxRanks; ++p) cd.base[p] = p < c->ws ? c->peer[p] : nullptr;
   cd.rank = c->rank; cd.ws = c->ws;
+  if (one_shot < 0 || one_shot > 2) return set_error(LIGER_ERR_INVALID, "allreduce_fused: one_shot must be 0, 1 or 2");
   int lo = row_begin, hi = row_end;
-  if (!one_shot) {
+  if (one_shot != 1) {
     const int rpr = (m + c->ws - 1) / c->ws;
     lo = row_begin > c->rank * rpr ? row_begin : c->rank * rpr;
     const int own_hi = (c->rank + 1) * rpr < m ? (c->rank + 1) * rpr : m;
@@ -390,6 +415,7 @@ extern "C" int liger_allreduce_fused(liger_comm* c, int channel, size_t partial_
   const uint32_t e_out = ++c->epoch[channel];
   allreduce_fused_kernel<<<grid, kArThreads, 0, (cudaStream_t)stream>>>(
       cd, channel, kFlagRegionBytes + partial_off, kFlagRegionBytes + out_off, (const __half*)residual_in, (__half*)hidden, (const __half*)bias,
-      (const __half*)gamma, (const __half*)beta, n, lo, hi, one_shot, e_in, e_out, c->done + channel, dev->status_dev);
+      (const __half*)gamma, (const __half*)beta, n, lo, hi, one_shot, e_in, e_out, c->done + channel,
+      c->stamps + 8 * channel, dev->status_dev);
   return check_launch("allreduce_fused_kernel");
 }

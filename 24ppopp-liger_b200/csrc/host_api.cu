@@ -155,13 +155,33 @@ extern "C" int liger_model_forward_host(liger_model* m, const void* host_input, 
   if (!m || !host_input || !host_output) return liger::set_error(LIGER_ERR_INVALID, "model_forward_host: null argument");
   if (batch < 1 || seq_len < 1 || (size_t)batch * seq_len > m->model->tokens_max())
     return liger::set_error(LIGER_ERR_INVALID, "model_forward_host: batch/seq outside the configured maximum");
-  const size_t bytes = (size_t)batch * seq_len * m->model->H * 2;
+  Bert_Model& b = *m->model;
+  const int M = batch * seq_len, H = b.H, ws = m->sp.world_size, rank = m->sp.world_rank;
+  const size_t bytes = (size_t)M * H * 2;
   cudaStream_t s = (cudaStream_t)stream;
-  LIGER_CUDA_TRY(cudaMemcpyAsync(m->io_in, host_input, bytes, cudaMemcpyHostToDevice, s));
-  const int n = liger_model_forward(m, m->io_in, m->io_out, batch, seq_len, slot, stream);
+  if (slot < 0) { slot = b.next_slot; b.next_slot = (b.next_slot + 1) % (int)b.slots.size(); }
+  if (slot >= (int)b.slots.size()) return liger::set_error(LIGER_ERR_INVALID, "model_forward_host: slot %d", slot);
+  if (ws == 1) {
+    LIGER_CUDA_TRY(cudaMemcpyAsync(m->io_in, host_input, bytes, cudaMemcpyHostToDevice, s));
+    const int n = liger_model_forward(m, m->io_in, m->io_out, batch, seq_len, slot, stream);
+    if (n < 0) return n;
+    LIGER_CUDA_TRY(cudaMemcpyAsync(host_output, m->io_out, bytes, cudaMemcpyDeviceToHost, s));
+    return n;
+  }
+  // upload this rank's rows only, then gather the rest over peer memory
+  Workspace& w = b.slots[slot];
+  const int rpr = (M + ws - 1) / ws;
+  const int lo = rank * rpr < M ? rank * rpr : M, hi = (rank + 1) * rpr < M ? (rank + 1) * rpr : M;
+  if (hi > lo)
+    LIGER_CUDA_TRY(cudaMemcpyAsync(w.partial + (size_t)lo * H, (const half_t*)host_input + (size_t)lo * H,
+                                   (size_t)(hi - lo) * H * 2, cudaMemcpyHostToDevice, s));
+  int rc = liger_allreduce_fused(m->sp.comm, slot, w.partial_off, w.xbuf_off, nullptr, nullptr, nullptr, nullptr, nullptr, M,
+                                 H, 0, M, 2, stream);
+  if (rc != LIGER_OK) return rc;
+  const int n = liger_model_forward(m, w.xbuf, m->io_out, batch, seq_len, slot, stream);
   if (n < 0) return n;
-  LIGER_CUDA_TRY(cudaMemcpyAsync(host_output, m->io_out, bytes, cudaMemcpyDeviceToHost, s));
-  return n;
+  if (rank == 0) LIGER_CUDA_TRY(cudaMemcpyAsync(host_output, m->io_out, bytes, cudaMemcpyDeviceToHost, s));
+  return n + 1;
 }
 
 extern "C" int liger_model_set_kernel_timing(liger_model* m, int enable) {

@@ -253,6 +253,14 @@ LIGER_API int liger_comm_rank(liger_comm* comm);
 LIGER_API int liger_comm_world_size(liger_comm* comm);
 
 /*
+ * Where the fused all-reduce launches of `channel` spent their time since the last reset, summed over
+ * launches, in microseconds: out_us[0] waiting for peers at the entry barrier (skew between ranks),
+ * out_us[1] reducing / normalising / storing, out_us[2] waiting at the exit barrier; out_us[3] = number
+ * of launches.  Synchronises the device copy; call it outside timed regions.
+ */
+LIGER_API int liger_comm_timing(liger_comm* comm, int channel, int reset, double out_us[4]);
+
+/*
  * All-reduce (sum over ranks) of the row-parallel partials, fused with what follows it in the layer.
  * Replaces Allreduce (src/layer/func_wrapper.h:40-43, bound at src/layer/linear.h:55-60) together
  * with the residual / LayerNorm kernel after it (Layer_Norm, src/layer/func_wrapper.h:110-114, or
@@ -268,7 +276,9 @@ LIGER_API int liger_comm_world_size(liger_comm* comm);
  * preceded and followed by a cross-rank barrier on flag set `channel`, so that a kernel launched
  * after this one on the same stream sees all rows.  With one_shot != 0 every rank instead reduces
  * all rows itself and stores only locally (latency-bound sizes; hidden is then updated for all
- * rows on every rank).  Waits on peers are bounded; on timeout the device status word is set.
+ * rows on every rank).  one_shot == 2 turns the call into an all-gather: each rank's own rows of its
+ * partial are taken as they are (no sum over peers) and stored to every rank.
+ * Waits on peers are bounded; on timeout the device status word is set.
  * N % 8 == 0, N <= 16384.  row_begin / row_end allow the collective to be issued in slices
  * (decompose_comm_callback, src/utils.h:262-281).
  */
@@ -331,8 +341,11 @@ LIGER_API int liger_model_destroy(liger_model* model);
  */
 LIGER_API int liger_model_forward(liger_model* model, const void* input, void* output, int batch, int seq_len, int slot,
                                   void* stream);
-/* Same with HOST buffers: copies the input to the device, runs the pass, copies the result back,
- * all on `stream`; returns after enqueueing (synchronise the stream before reading host_output). */
+/* Same with HOST buffers, all on `stream`; returns after enqueueing (synchronise the stream before
+ * reading host_output).  world_size == 1: the whole input is copied to the device and the whole
+ * result back.  world_size > 1: every rank passes the same full host input but uploads only its
+ * own 1/world_size of the rows, which an all-gather over peer memory completes on every GPU; the
+ * result is copied to host_output on rank 0 only (other ranks leave host_output untouched). */
 LIGER_API int liger_model_forward_host(liger_model* model, const void* host_input, void* host_output, int batch,
                                        int seq_len, int slot, void* stream);
 /*

@@ -122,6 +122,14 @@ def _tp_worker(rank, world, port, case, results):
     for rep in range(2):
         liger.check(lib.liger_model_forward(model, ptr(x), ptr(out), c["B"], c["S"], rep % 2, stream_ptr()))
         torch.cuda.synchronize()
+    # host-buffer entry point: every rank uploads its rows, rank 0 receives the result
+    hin = x.cpu().pin_memory()
+    hout = torch.zeros((M, H), dtype=torch.float16).pin_memory()
+    liger.check(lib.liger_model_forward_host(model, C.c_void_p(hin.data_ptr()), C.c_void_p(hout.data_ptr()), c["B"], c["S"],
+                                             1, stream_ptr()))
+    torch.cuda.synchronize()
+    if rank == 0:
+        assert torch.equal(hout, out.cpu())
     st = (C.c_uint * 4)()
     assert lib.liger_device_status(C.byref(st)) == 0, list(st)
     results[rank] = to_np(out)
