@@ -95,7 +95,22 @@ __device__ __forceinline__ bool barrier_wait(const CommDev& c, int channel, uint
   return *s_fail == 0;
 }
 
-__global__ void __launch_bounds__(kArThreads)
+// Entry barrier of a fused all-reduce as a kernel of its own (one warp): "every rank's partial is
+// complete and visible".  Keeping the wait out of the data kernel means that no more than one tiny
+// CTA per collective ever spins on a peer, so a collective that is ahead of its peers cannot
+// occupy the SMs that the peers' (or this rank's other streams') GEMMs need in order to catch up.
+__global__ void allreduce_entry_barrier_kernel(CommDev c, int channel, uint32_t epoch_in, unsigned long long* stamps,
+                                               DeviceStatus* st) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  const unsigned long long t_enter = globaltimer_ns();
+  barrier_signal(c, channel, epoch_in);
+  barrier_wait(c, channel, epoch_in, &s_fail, st, 0x200u);
+  if (threadIdx.x == 0) { stamps[0] = t_enter; stamps[1] = globaltimer_ns(); stamps[4] += stamps[1] - t_enter; }
+}
+
+__global__ void __launch_bounds__(kArThreads, 2)
 allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t out_off,
                        const __half* residual_in, __half* hidden,
                        const __half* __restrict__ bias, const __half* __restrict__ gamma,
@@ -107,11 +122,8 @@ allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t out_of
   if (threadIdx.x == 0) { s_fail = 0; s_last = 0; }
   __syncthreads();
 
-  // ---- entry barrier: every rank's partial is complete and visible ----
-  const unsigned long long t_enter = globaltimer_ns();
-  if (blockIdx.x == 0) barrier_signal(c, channel, epoch_in);
-  if (!barrier_wait(c, channel, epoch_in, &s_fail, st, 0x200u)) return;
-  const unsigned long long t_go = globaltimer_ns();
+  // (the entry barrier ran as allreduce_entry_barrier_kernel, earlier on this stream)
+  (void)epoch_in;
 
   const int nvec = n >> 3;
   for (int row = row_lo + blockIdx.x; row < row_hi; row += gridDim.x) {
@@ -121,9 +133,14 @@ allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t out_of
     for (int i = 0; i < kArMaxVec; ++i)
 #pragma unroll
       for (int j = 0; j < 8; ++j) v[i][j] = 0.0f;
-    const int nsum = one_shot == 2 ? 1 : c.ws;  // gather mode: only this rank's own rows are read
+    // Summation order: starts at rank (row mod ws) and continues cyclically.  It depends only on the
+    // row, not on which rank owns it or on how a batch was split, so results are reproducible across
+    // one-shot / two-shot and across micro-batching, and different rows start at different peers,
+    // which spreads the reads over all links.  Gather mode reads only this rank's own rows.
+    const int nsum = one_shot == 2 ? 1 : c.ws;
+    const int first = one_shot == 2 ? c.rank : row % c.ws;
     for (int kx = 0; kx < nsum; ++kx) {
-      int p = c.rank + kx;
+      int p = first + kx;
       if (p >= c.ws) p -= c.ws;
       const __half* src = reinterpret_cast<const __half*>(c.base[p] + partial_off) + roff;
 #pragma unroll
@@ -249,8 +266,8 @@ allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t out_of
     if (threadIdx.x == 0) {
       // stamps of the last CTA to finish: wait for peers at entry / own work / wait for peers at exit
       const unsigned long long t_exit = globaltimer_ns();
-      stamps[0] = t_enter; stamps[1] = t_go; stamps[2] = t_work; stamps[3] = t_exit;
-      stamps[4] += t_go - t_enter; stamps[5] += t_work - t_go; stamps[6] += t_exit - t_work; stamps[7] += 1ull;
+      stamps[2] = t_work; stamps[3] = t_exit;
+      stamps[5] += t_work - stamps[1]; stamps[6] += t_exit - t_work; stamps[7] += 1ull;
     }
   }
 }
@@ -413,6 +430,10 @@ extern "C" int liger_allreduce_fused(liger_comm* c, int channel, size_t partial_
   if (grid < 1) grid = 1;
   const uint32_t e_in = ++c->epoch[channel];
   const uint32_t e_out = ++c->epoch[channel];
+  allreduce_entry_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(cd, channel, e_in, c->stamps + 8 * channel,
+                                                                     dev->status_dev);
+  int rc = check_launch("allreduce_entry_barrier_kernel");
+  if (rc != LIGER_OK) return rc;
   allreduce_fused_kernel<<<grid, kArThreads, 0, (cudaStream_t)stream>>>(
       cd, channel, kFlagRegionBytes + partial_off, kFlagRegionBytes + out_off, (const __half*)residual_in, (__half*)hidden, (const __half*)bias,
       (const __half*)gamma, (const __half*)beta, n, lo, hi, one_shot, e_in, e_out, c->done + channel,

@@ -22,6 +22,10 @@ struct liger_model {
   half_t* io_out = nullptr;
   int device = 0;
   bool timing = false;
+  int micro_batches = 1;
+  std::vector<cudaStream_t> aux_streams;
+  cudaEvent_t ev_fork = nullptr;
+  std::vector<cudaEvent_t> ev_join;
   std::vector<cudaEvent_t> ev_pool;                      // reusable events
   std::vector<std::pair<int, std::pair<cudaEvent_t, cudaEvent_t>>> ev_rec;  // (name, (before, after))
   cudaEvent_t get_event() {
@@ -128,26 +132,100 @@ extern "C" int liger_model_destroy(liger_model* m) {
   return LIGER_OK;
 }
 
+// One request, kernels in order on one stream.
+static int forward_sequential(liger_model* m, const void* input, void* output, int batch, int seq_len, int slot,
+                              void* stream) {
+  std::vector<FuncWrap> vec = m->model->forward(input, output, batch, seq_len, slot);
+  DynamicNvInitParam dp;
+  dp.stream = stream;
+  int n = 0;
+  for (auto& f : vec) {
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    if (m->timing) { e0 = m->get_event(); e1 = m->get_event(); cudaEventRecord(e0, (cudaStream_t)stream); }
+    const int rc = f.callback(dp);
+    if (m->timing) { cudaEventRecord(e1, (cudaStream_t)stream); m->ev_rec.push_back({f.name, {e0, e1}}); }
+    if (rc != LIGER_OK) return rc;
+    ++n;
+  }
+  return n;
+}
+
+// The batch split into `mb` micro-requests, each on its own stream and workspace slot, launched
+// segment by segment in round-robin order: while one micro-request's all-reduce is on the wire the
+// other one's GEMMs keep the tensor cores busy -- Liger's interleaving of communication with other
+// requests' computation (src/schedule.h:221-278), applied statically to the halves of one batch.
+static int forward_interleaved(liger_model* m, const void* input, void* output, int batch, int seq_len, int slot0, int mb,
+                               void* stream) {
+  cudaStream_t caller = (cudaStream_t)stream;
+  while ((int)m->aux_streams.size() < mb) {
+    cudaStream_t s = nullptr;
+    LIGER_CUDA_TRY(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    m->aux_streams.push_back(s);
+    cudaEvent_t e = nullptr;
+    LIGER_CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    m->ev_join.push_back(e);
+  }
+  if (!m->ev_fork) LIGER_CUDA_TRY(cudaEventCreateWithFlags(&m->ev_fork, cudaEventDisableTiming));
+  const int sub = batch / mb;
+  const size_t rows = (size_t)sub * seq_len, H = m->model->H;
+  std::vector<std::vector<FuncWrap>> vecs;
+  for (int i = 0; i < mb; ++i)
+    vecs.push_back(m->model->forward((const half_t*)input + i * rows * H, (half_t*)output + i * rows * H, sub, seq_len,
+                                     slot0 + i));
+  LIGER_CUDA_TRY(cudaEventRecord(m->ev_fork, caller));
+  for (int i = 0; i < mb; ++i) LIGER_CUDA_TRY(cudaStreamWaitEvent(m->aux_streams[i], m->ev_fork, 0));
+  std::vector<size_t> cur(mb, 0);
+  int n = 0;
+  bool more = true;
+  while (more) {
+    more = false;
+    for (int i = 0; i < mb; ++i) {
+      std::vector<FuncWrap>& v = vecs[i];
+      if (cur[i] >= v.size()) continue;
+      DynamicNvInitParam dp;
+      dp.stream = m->aux_streams[i];
+      dp.index = i;
+      // one segment: a maximal run of kernels of the same class (communication / not)
+      const bool comm = v[cur[i]].type == COMMUNICATION;
+      while (cur[i] < v.size() && (v[cur[i]].type == COMMUNICATION) == comm) {
+        const int rc = v[cur[i]].callback(dp);
+        if (rc != LIGER_OK) return rc;
+        ++cur[i];
+        ++n;
+      }
+      if (cur[i] < v.size()) more = true;
+    }
+  }
+  for (int i = 0; i < mb; ++i) {
+    LIGER_CUDA_TRY(cudaEventRecord(m->ev_join[i], m->aux_streams[i]));
+    LIGER_CUDA_TRY(cudaStreamWaitEvent(caller, m->ev_join[i], 0));
+  }
+  return n;
+}
+
 extern "C" int liger_model_forward(liger_model* m, const void* input, void* output, int batch, int seq_len, int slot,
                                    void* stream) {
   if (!m || !input || !output) return liger::set_error(LIGER_ERR_INVALID, "model_forward: null argument");
   try {
-    std::vector<FuncWrap> vec = m->model->forward(input, output, batch, seq_len, slot);
-    DynamicNvInitParam dp;
-    dp.stream = stream;
-    int n = 0;
-    for (auto& f : vec) {
-      cudaEvent_t e0 = nullptr, e1 = nullptr;
-      if (m->timing) { e0 = m->get_event(); e1 = m->get_event(); cudaEventRecord(e0, (cudaStream_t)stream); }
-      const int rc = f.callback(dp);
-      if (m->timing) { cudaEventRecord(e1, (cudaStream_t)stream); m->ev_rec.push_back({f.name, {e0, e1}}); }
-      if (rc != LIGER_OK) return rc;
-      ++n;
+    const int mb = m->micro_batches;
+    if (mb > 1 && m->sp.world_size > 1 && !m->timing && batch % mb == 0) {
+      Bert_Model& b = *m->model;
+      if (slot < 0) { slot = b.next_slot; b.next_slot = (b.next_slot + mb) % (int)b.slots.size(); }
+      if (slot + mb > (int)b.slots.size())
+        return liger::set_error(LIGER_ERR_INVALID, "model_forward: %d micro-batches from slot %d need %d workspace slots", mb,
+                                slot, slot + mb);
+      return forward_interleaved(m, input, output, batch, seq_len, slot, mb, stream);
     }
-    return n;
+    return forward_sequential(m, input, output, batch, seq_len, slot, stream);
   } catch (const std::exception& e) {
     return liger::set_error(LIGER_ERR_INVALID, "model_forward: %s", e.what());
   }
+}
+
+extern "C" int liger_model_set_micro_batches(liger_model* m, int micro_batches) {
+  if (!m || micro_batches < 1 || micro_batches > 8) return liger::set_error(LIGER_ERR_INVALID, "model_set_micro_batches: 1..8");
+  m->micro_batches = micro_batches;
+  return LIGER_OK;
 }
 
 extern "C" int liger_model_forward_host(liger_model* m, const void* host_input, void* host_output, int batch, int seq_len,

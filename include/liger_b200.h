@@ -268,7 +268,7 @@ LIGER_API int liger_comm_timing(liger_comm* comm, int channel, int reset, double
  *
  * Every rank holds its partial [M, N] fp16 at byte offset partial_off of its segment.  Rank r owns
  * rows [r*ceil(M/ws), (r+1)*ceil(M/ws)).  For each owned row in [row_begin, row_end):
- *     t = sum_p partial_p[row]            fp32; order: own partial first, then increasing rank, cyclic
+ *     t = sum_p partial_p[row]            fp32; order: p = row mod ws first, then increasing rank, cyclic
  *     if hidden:  t += residual_in[row] + bias ; hidden[row] = fp16(t)   (residual stream, local, owner
  *                 rows; residual_in may equal hidden, or be NULL to mean hidden)
  *     if gamma:   o = LayerNorm(fp16(t)) * gamma + beta   else   o = fp16(t)
@@ -341,6 +341,18 @@ LIGER_API int liger_model_destroy(liger_model* model);
  */
 LIGER_API int liger_model_forward(liger_model* model, const void* input, void* output, int batch, int seq_len, int slot,
                                   void* stream);
+/*
+ * Interleaving inside one request.  With micro_batches = n > 1 and world_size > 1, a forward pass
+ * whose batch divides by n is split into n micro-requests (consecutive groups of sequences) that
+ * run on n internal streams and n consecutive workspace slots starting at `slot`, launched
+ * segment by segment in turn, so that the all-reduces of one micro-request overlap the GEMMs of
+ * the others; the caller's stream waits for all of them.  This is the reference scheduler's
+ * interleaving of one request's communication with other requests' computation
+ * (Scheduler::run_stream_sync, src/schedule.h:221-278) applied to the halves of a single batch.
+ * Results are identical to the un-split pass (rows are independent across sequences).
+ */
+LIGER_API int liger_model_set_micro_batches(liger_model* model, int micro_batches);
+
 /* Same with HOST buffers, all on `stream`; returns after enqueueing (synchronise the stream before
  * reading host_output).  world_size == 1: the whole input is copied to the device and the whole
  * result back.  world_size > 1: every rank passes the same full host input but uploads only its
