@@ -7,7 +7,7 @@ use it, only provides device memory, streams and process-group plumbing.
 There is no CPU fallback: `lib()` raises if the CUDA library has not been built, and every
 compute entry point fails without a CUDA device.
 """
-from . import capi
+from . import build, capi
 from .build import build_all, LIB_PATH
 from .capi import lib, check, LigerError, GemmArgs, ModelConfig, default_config
 

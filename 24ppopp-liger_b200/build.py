@@ -43,6 +43,35 @@ def needs_build():
     return any(os.path.getmtime(p) > t for p in _deps())
 
 
+HOST = os.path.join(HERE, "host")
+BIN_DIR = os.path.join(HERE, "bin")
+MAIN_PATH = os.path.join(BIN_DIR, "liger_main")
+MPIRUN_PATH = os.path.join(BIN_DIR, "liger_mpirun")
+SHIM_PATH = os.path.join(HERE, "libliger_mpi_shim.so")
+
+
+def build_host(force=False):
+    """The serving executable (host/main.cu), the shared-memory MPI stand-in and its launcher."""
+    os.makedirs(BIN_DIR, exist_ok=True)
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    shim_src = os.path.join(HOST, "mpi_shim", "mpi_shim.cc")
+    jobs = [
+        (SHIM_PATH, [shim_src], ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-o", SHIM_PATH, shim_src, "-lrt", "-lpthread"]),
+        (MPIRUN_PATH, [os.path.join(HOST, "mpi_shim", "liger_mpirun.cc")],
+         ["g++", "-O2", "-std=c++17", "-o", MPIRUN_PATH, os.path.join(HOST, "mpi_shim", "liger_mpirun.cc")]),
+        (MAIN_PATH, _deps() + [os.path.join(HOST, f) for f in os.listdir(HOST) if f.endswith((".h", ".cu"))] + [LIB_PATH],
+         [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O2", "-std=c++17",
+          "-I", os.path.join(HOST, "mpi_shim"), "-o", MAIN_PATH, os.path.join(HOST, "main.cu"), shim_src,
+          "-L", HERE, "-lliger_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/..", "-lrt", "-lpthread"]),
+    ]
+    for out, deps, cmd in jobs:
+        if force or not os.path.exists(out) or any(os.path.getmtime(d) > os.path.getmtime(out) for d in deps if os.path.exists(d)):
+            res = subprocess.run(cmd, cwd=HERE, capture_output=True, text=True)
+            if res.returncode != 0:
+                raise RuntimeError(" ".join(cmd) + " failed:\n" + res.stdout + res.stderr)
+    return MAIN_PATH
+
+
 def build_all(force=False, verbose=False):
     """Compile csrc/ -> libliger_b200.so. Returns the library path."""
     if not force and not needs_build():

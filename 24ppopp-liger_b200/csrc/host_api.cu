@@ -357,6 +357,28 @@ extern "C" int liger_serve(liger_model* m, int mode, liger_bcast_int_fn bcast, l
   }
 }
 
+extern "C" int liger_profile_rewrite(const char* in_path, const char* out_path, int is_sub, int* entries, double* duration_sum) {
+  if (!in_path) return liger::set_error(LIGER_ERR_INVALID, "profile_rewrite: null path");
+  try {
+    int n = 0;
+    double sum = 0.0;
+    if (is_sub) {
+      SubDict d = SubFileToDict(in_path);
+      for (auto& e : d) { ++n; for (float v : e.second) sum += v; }
+      if (out_path) SubDictToFile(d, out_path);
+    } else {
+      MainDict d = MainFileToDict(in_path);
+      for (auto& e : d) { ++n; sum += e.second; }
+      if (out_path) MainDictToFile(d, out_path);
+    }
+    if (entries) *entries = n;
+    if (duration_sum) *duration_sum = sum;
+    return LIGER_OK;
+  } catch (const std::exception& e) {
+    return liger::set_error(LIGER_ERR_INVALID, "profile_rewrite: %s", e.what());
+  }
+}
+
 // ---- the scheduler on a simulated device --------------------------------------------------------------
 namespace {
 
@@ -366,6 +388,7 @@ struct SimModel {
   std::vector<liger_sim_kernel> kernels;
   double slice_overhead_ms;
   int next_request = 0;
+  double device_slowdown = 1.0;  // what the device really takes relative to the profiled durations
 
   float scaled(float base, int bs, int sq) const {
     return base * (float)((double)bs * sq / ((double)bp.max_batch_size * bp.max_seq_len));
@@ -378,12 +401,13 @@ struct SimModel {
         const float dur = scaled(kernels[k].duration_ms, bs, sq);
         const int tag = (req << 16) | (l << 8) | (int)k;
         SimRuntime* r = rt;
+        const float real = (float)(dur * device_slowdown);
         FuncWrap f((int)k, dur, (layer_type)kernels[k].type,
-                   [r, dur, tag](const DynamicNvInitParam& d) { r->launch(d.stream, dur, tag); return LIGER_OK; });
+                   [r, real, tag](const DynamicNvInitParam& d) { r->launch(d.stream, real, tag); return LIGER_OK; });
         if (kernels[k].type == GEMM || kernels[k].type == COMMUNICATION) {
-          const double ovh = slice_overhead_ms;
-          f.slicer = [r, dur, tag, ovh](int ub, int ue, int factor) {
-            const float sd = (float)(ovh + (double)dur * (ue - ub) / factor);
+          const double ovh = slice_overhead_ms, slow = device_slowdown;
+          f.slicer = [r, dur, tag, ovh, slow](int ub, int ue, int factor) {
+            const float sd = (float)((ovh + (double)dur * (ue - ub) / factor) * slow);
             const int stag = tag | (ub << 24) | (ue << 28);
             return [r, sd, stag](const DynamicNvInitParam& d) { r->launch(d.stream, sd, stag); return LIGER_OK; };
           };
@@ -399,17 +423,30 @@ struct SimModel {
 extern "C" int liger_sim_serve(const liger_model_config* cfg, const liger_sim_kernel* layer_kernels, int kernels_per_layer,
                                int mode, double overlap_rate, double slice_overhead_ms, liger_sim_launch* log,
                                int log_capacity, int* log_count, liger_serving_metrics* metrics) {
+  return liger_sim_serve_rank(cfg, layer_kernels, kernels_per_layer, mode, overlap_rate, slice_overhead_ms, 0, 1, nullptr,
+                              nullptr, nullptr, 0.0, 1.0, log, log_capacity, log_count, metrics);
+}
+
+extern "C" int liger_sim_serve_rank(const liger_model_config* cfg, const liger_sim_kernel* layer_kernels,
+                                    int kernels_per_layer, int mode, double overlap_rate, double slice_overhead_ms, int rank,
+                                    int world_size, liger_bcast_int_fn bcast, liger_barrier_fn barrier, void* ctx,
+                                    double host_skew_ms, double device_slowdown, liger_sim_launch* log, int log_capacity,
+                                    int* log_count, liger_serving_metrics* metrics) {
   int rc = validate(cfg);
   if (rc != LIGER_OK) return rc;
   if (!layer_kernels || kernels_per_layer < 1 || kernels_per_layer > 255 || cfg->factor > 15 || cfg->layer_num > 255)
     return liger::set_error(LIGER_ERR_INVALID, "sim_serve: bad kernel list (<= 255 kernels, factor <= 15)");
   try {
+    if (world_size < 1 || rank < 0 || rank >= world_size || (world_size > 1 && !bcast))
+      return liger::set_error(LIGER_ERR_INVALID, "sim_serve: bad rank / world_size / callbacks");
     SimRuntime rt;
     rt.overlap_rate = overlap_rate;
-    Coordinator coord;
-    SimModel model{&rt, to_params(*cfg), std::vector<liger_sim_kernel>(layer_kernels, layer_kernels + kernels_per_layer),
-                   slice_overhead_ms};
-    StaticNvInitParam sp(0, 1, nullptr, 1);
+    rt.host_advance_ms(host_skew_ms);
+    CallbackCoordinator coord(rank, world_size, bcast, barrier, ctx);
+    std::vector<liger_sim_kernel> kv(layer_kernels, layer_kernels + kernels_per_layer);
+    SimModel model{&rt, to_params(*cfg), kv, slice_overhead_ms};
+    model.device_slowdown = device_slowdown > 0.0 ? device_slowdown : 1.0;
+    StaticNvInitParam sp(rank, world_size, nullptr, 1);
     Scheduler<SimModel> scheduler(&model, model.bp, sp, nullptr, nullptr, &rt, &coord);
     // the cost model: isolated durations, as a profile run on this simulated device would measure
     const std::vector<Request> reqs = make_requests(model.bp, model.bp.num_requests, model.bp.seed);

@@ -406,6 +406,15 @@ LIGER_API int liger_serve(liger_model* model, int mode, liger_bcast_int_fn bcast
                           const char* profile_dir, int print, liger_serving_metrics* metrics);
 
 /*
+ * Profile files (the scheduler's cost model; format of MainDictToFile / SubDictToFile,
+ * src/utils.h:106-215).  liger_profile_rewrite() parses `in_path` (is_sub = 0: scalar durations,
+ * 1: arrays of factor-1 durations) and writes it back through the library's writer; entries and
+ * the sum of all durations are returned.  Malformed input (the reference's reader throws) gives
+ * LIGER_ERR_INVALID with the parse position in liger_last_error().  out_path may be NULL.
+ */
+LIGER_API int liger_profile_rewrite(const char* in_path, const char* out_path, int is_sub, int* entries, double* duration_sum);
+
+/*
  * The scheduling logic on a simulated device (no GPU): a layer is given as kernels_per_layer
  * (type, milliseconds at max_batch*max_seq tokens) pairs, durations scale with the token count, a
  * GEMM slice of n/factor costs slice_overhead_ms + n/factor of the whole, and two kernels running
@@ -422,6 +431,15 @@ LIGER_API int liger_sim_serve(const liger_model_config* cfg, const liger_sim_ker
                               int kernels_per_layer, int mode, double overlap_rate, double slice_overhead_ms,
                               liger_sim_launch* log, int log_capacity, int* log_count,
                               liger_serving_metrics* metrics);
+/* The same as one rank of `world_size`: admissions are decided by rank 0 and received through
+ * `bcast` (as in liger_serve); this rank's host clock runs `host_skew_ms` ahead, and its device is
+ * `device_slowdown` times slower, so that ranks would admit at different moments if they decided
+ * on their own. */
+LIGER_API int liger_sim_serve_rank(const liger_model_config* cfg, const liger_sim_kernel* layer_kernels,
+                                   int kernels_per_layer, int mode, double overlap_rate, double slice_overhead_ms,
+                                   int rank, int world_size, liger_bcast_int_fn bcast, liger_barrier_fn barrier, void* ctx,
+                                   double host_skew_ms, double device_slowdown, liger_sim_launch* log, int log_capacity,
+                                   int* log_count, liger_serving_metrics* metrics);
 
 #ifdef __cplusplus
 }
