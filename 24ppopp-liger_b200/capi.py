@@ -5,7 +5,7 @@ import os
 from .build import LIB_PATH
 
 LIGER_OK = 0
-EPI_STORE, EPI_GELU, EPI_GEGLU, EPI_QKV_SPLIT, EPI_RESIDUAL = 0, 1, 2, 3, 4
+EPI_STORE, EPI_GELU, EPI_GEGLU, EPI_QKV_SPLIT, EPI_RESIDUAL, EPI_SCATTER = 0, 1, 2, 3, 4, 5
 DEV_TIMEOUT, DEV_BOUNDS = 1, 2
 
 
@@ -24,6 +24,7 @@ class GemmArgs(C.Structure):
         ("n_begin", C.c_int), ("n_end", C.c_int), ("epilogue", C.c_int),
         ("seq_len", C.c_int), ("heads", C.c_int), ("head_dim", C.c_int),
         ("kv_stride", C.c_int), ("kv_pos", C.c_int),
+        ("scatter_comm", C.c_void_p), ("scatter_off", C.c_size_t),
     ]
 
 

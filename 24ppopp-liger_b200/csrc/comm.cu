@@ -15,12 +15,11 @@
 #include <cstring>
 #include <vector>
 
+#include "comm_internal.h"
 #include "runtime.h"
 
 namespace liger {
 
-constexpr int kMaxRanks = LIGER_COMM_MAX_RANKS;
-constexpr size_t kFlagRegionBytes = 65536;  // flags live in front of the data region
 constexpr int kFlagStrideWords = 32;        // one 128-byte line per (channel, peer) flag
 constexpr int kArThreads = 256;
 constexpr int kArMaxVec = 8;
@@ -44,18 +43,6 @@ static_assert(sizeof(HandleBlob) <= LIGER_COMM_HANDLE_BYTES, "handle blob too la
 constexpr uint32_t kHandleMagic = 0x4c474843u;
 
 }  // namespace liger
-
-struct liger_comm {
-  int rank = 0, ws = 1, channels = 1, device = 0;
-  size_t data_bytes = 0, seg_bytes = 0;
-  uint8_t* local = nullptr;
-  uint8_t* peer[liger::kMaxRanks] = {};
-  bool ipc_open[liger::kMaxRanks] = {};
-  bool connected = false;
-  std::vector<uint32_t> epoch;   // per channel, host side
-  unsigned int* done = nullptr;  // per channel CTA-completion counters (device)
-  unsigned long long* stamps = nullptr;  // per channel: 4 globaltimer stamps of the last launch + 4 running sums
-};
 
 namespace liger {
 
@@ -114,7 +101,8 @@ __global__ void __launch_bounds__(kArThreads, 2)
 allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t out_off,
                        const __half* residual_in, __half* hidden,
                        const __half* __restrict__ bias, const __half* __restrict__ gamma,
-                       const __half* __restrict__ beta, int n, int row_lo, int row_hi, int one_shot, uint32_t epoch_in,
+                       const __half* __restrict__ beta, int n, int row_lo, int row_hi, int one_shot, int rows_per_rank,
+                       uint32_t epoch_in,
                        uint32_t epoch_out, unsigned int* done_counter, unsigned long long* stamps, DeviceStatus* st) {
   __shared__ float red[32];
   __shared__ int s_fail;
@@ -142,7 +130,11 @@ allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t out_of
     for (int kx = 0; kx < nsum; ++kx) {
       int p = first + kx;
       if (p >= c.ws) p -= c.ws;
-      const __half* src = reinterpret_cast<const __half*>(c.base[p] + partial_off) + roff;
+      // mode 3: the producing GEMMs already stored every rank's rows for this owner into local slots
+      const __half* src = one_shot == 3
+                              ? reinterpret_cast<const __half*>(c.base[c.rank] + partial_off) +
+                                    ((size_t)p * rows_per_rank + (row - c.rank * rows_per_rank)) * n
+                              : reinterpret_cast<const __half*>(c.base[p] + partial_off) + roff;
 #pragma unroll
       for (int i = 0; i < kArMaxVec; ++i) {
         const int idx = threadIdx.x + i * kArThreads;
@@ -403,7 +395,9 @@ extern "C" int liger_allreduce_fused(liger_comm* c, int channel, size_t partial_
                      kArThreads * kArMaxVec * 8);
   if (row_begin < 0 || row_end > m || row_begin > row_end) return set_error(LIGER_ERR_INVALID, "allreduce_fused: bad row range");
   const size_t bytes = (size_t)m * n * 2;
-  if (partial_off % 16 || out_off % 16 || partial_off + bytes > c->data_bytes || out_off + bytes > c->data_bytes)
+  const int rpr_all = (m + c->ws - 1) / c->ws;
+  const size_t in_bytes = one_shot == 3 ? (size_t)c->ws * rpr_all * n * 2 : bytes;
+  if (partial_off % 16 || out_off % 16 || partial_off + in_bytes > c->data_bytes || out_off + bytes > c->data_bytes)
     return set_error(LIGER_ERR_INVALID, "allreduce_fused: offsets must be 16-byte aligned and inside the %zu-byte data region",
                      c->data_bytes);
   if ((gamma == nullptr) != (beta == nullptr)) return set_error(LIGER_ERR_INVALID, "allreduce_fused: gamma and beta go together");
@@ -415,7 +409,7 @@ extern "C" int liger_allreduce_fused(liger_comm* c, int channel, size_t partial_
   CommDev cd;
   for (int p = 0; p < kMaxRanks; ++p) cd.base[p] = p < c->ws ? c->peer[p] : nullptr;
   cd.rank = c->rank; cd.ws = c->ws;
-  if (one_shot < 0 || one_shot > 2) return set_error(LIGER_ERR_INVALID, "allreduce_fused: one_shot must be 0, 1 or 2");
+  if (one_shot < 0 || one_shot > 3) return set_error(LIGER_ERR_INVALID, "allreduce_fused: one_shot must be 0, 1, 2 or 3");
   int lo = row_begin, hi = row_end;
   if (one_shot != 1) {
     const int rpr = (m + c->ws - 1) / c->ws;
@@ -436,7 +430,7 @@ extern "C" int liger_allreduce_fused(liger_comm* c, int channel, size_t partial_
   if (rc != LIGER_OK) return rc;
   allreduce_fused_kernel<<<grid, kArThreads, 0, (cudaStream_t)stream>>>(
       cd, channel, kFlagRegionBytes + partial_off, kFlagRegionBytes + out_off, (const __half*)residual_in, (__half*)hidden, (const __half*)bias,
-      (const __half*)gamma, (const __half*)beta, n, lo, hi, one_shot, e_in, e_out, c->done + channel,
+      (const __half*)gamma, (const __half*)beta, n, lo, hi, one_shot, rpr_all, e_in, e_out, c->done + channel,
       c->stamps + 8 * channel, dev->status_dev);
   return check_launch("allreduce_fused_kernel");
 }

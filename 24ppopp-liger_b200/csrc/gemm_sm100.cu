@@ -14,6 +14,7 @@
 //             scatter in registers, 16-byte fp16 stores; then `tmem_empty` lets the MMA warp
 //             reuse the accumulator, so the epilogue of tile i overlaps the MMAs of tile i+1.
 // All waits are bounded (common.cuh); a timeout sets the sticky status word and the CTA unwinds.
+#include "comm_internal.h"
 #include "runtime.h"
 
 namespace liger {
@@ -33,6 +34,10 @@ struct GemmParams {
   int seq_len, heads, head_dim;
   int kv_stride, kv_pos;
   int tiles_m, tiles_n, kblocks;
+  // LIGER_EPI_SCATTER: row r goes to rank r / rows_per_rank, into that rank's receive slot for this rank
+  uint8_t* peer[kMaxRanks];
+  size_t scatter_off;
+  int rank, rows_per_rank;
   DeviceStatus* status;
 };
 
@@ -99,6 +104,10 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, int row, int
         dst = p.qkv[which] + (((size_t)b * p.heads + head) * p.kv_stride + p.kv_pos + s) * p.head_dim + d;
       else
         dst = p.qkv[which] + (((size_t)b * p.heads + head) * p.seq_len + s) * p.head_dim + d;
+    } else if (p.epilogue == LIGER_EPI_SCATTER) {
+      const int owner = row / p.rows_per_rank;
+      const int local_row = p.rank * p.rows_per_rank + (row - owner * p.rows_per_rank);
+      dst = reinterpret_cast<__half*>(p.peer[owner] + p.scatter_off) + (size_t)local_row * p.ldc + col;
     } else {
       dst = p.c + (size_t)row * p.ldc + col;
     }
@@ -356,6 +365,19 @@ extern "C" int liger_gemm_fp16(const liger_gemm_args* args, void* stream) {
       p.seq_len = a.seq_len; p.heads = a.heads; p.head_dim = a.head_dim;
       p.kv_stride = a.kv_stride; p.kv_pos = a.kv_pos;
       break;
+    case LIGER_EPI_SCATTER: {
+      liger_comm* c = a.scatter_comm;
+      if (!c || !c->connected) return set_error(LIGER_ERR_INVALID, "gemm: scatter epilogue needs a connected communicator");
+      const int rpr = (a.m + c->ws - 1) / c->ws;
+      const size_t need = (size_t)c->ws * rpr * a.n * 2;
+      if (a.scatter_off % 16 || a.scatter_off + need > c->data_bytes)
+        return set_error(LIGER_ERR_INVALID, "gemm: scatter region [%zu, +%zu) must be 16-byte aligned and inside the %zu-byte data region",
+                         a.scatter_off, need, c->data_bytes);
+      for (int r = 0; r < kMaxRanks; ++r) p.peer[r] = r < c->ws ? c->peer[r] : nullptr;
+      p.scatter_off = kFlagRegionBytes + a.scatter_off;
+      p.rank = c->rank; p.rows_per_rank = rpr; p.ldc = a.n;
+      break;
+    }
     default:
       return set_error(LIGER_ERR_INVALID, "gemm: unknown epilogue %d", a.epilogue);
   }

@@ -223,6 +223,8 @@ class Bert_MHA {
       if (ws == 1 && post.residual_in) {  // no all-reduce to fuse the residual into: use the epilogue
         a.epilogue = LIGER_EPI_RESIDUAL; a.bias = post.bias; a.residual = post.residual_in; a.ldr = n;
         a.c = w.hidden;
+      } else if (ws > 1 && !is_one_shot(M, n)) {  // reduce-scatter by the epilogue's own stores
+        a.epilogue = LIGER_EPI_SCATTER; a.scatter_comm = SParam.comm; a.scatter_off = w.partial_off;
       }
       vec.push_back(make_gemm(2, 2.0f, a));
     }
@@ -238,7 +240,7 @@ class Bert_MHA {
       COMM_ARGS c;
       c.comm = sp.comm; c.channel = sh.slot; c.partial_off = w.partial_off; c.out_off = post.out_off;
       c.m = M; c.n = n; c.row_begin = 0; c.row_end = M;
-      c.one_shot = ((size_t)M * n * 2 <= kOneShotBytes) ? 1 : 0;
+      c.one_shot = is_one_shot(M, n) ? 1 : 3;
       if (post.residual_in) { c.residual_in = post.residual_in; c.hidden = w.hidden; c.bias = post.bias; }
       c.gamma = post.gamma; c.beta = post.beta;
       return make_comm(name, 2.0f, c);
@@ -249,7 +251,8 @@ class Bert_MHA {
       return liger_layernorm(src, g, b, out, M, n, d.stream);
     });
   }
-  static constexpr size_t kOneShotBytes = 1u << 20;
+  // payloads up to 1 MiB (decode) are latency bound: every rank reduces everything itself
+  static bool is_one_shot(int M, int n) { return (size_t)M * n * 2 <= ((size_t)1 << 20); }
 };
 
 // ---- MLP block: kernels 4-6 (src/layer/bert_layer.h:19-63) --------------------------------------------
@@ -290,6 +293,8 @@ class Bert_MLP {
       if (ws == 1 && post.residual_in) {
         a.epilogue = LIGER_EPI_RESIDUAL; a.bias = post.bias; a.residual = post.residual_in; a.ldr = n;
         a.c = post.direct_out ? post.direct_out : (void*)w.hidden;
+      } else if (ws > 1 && !Bert_MHA::is_one_shot(M, n)) {
+        a.epilogue = LIGER_EPI_SCATTER; a.scatter_comm = SParam.comm; a.scatter_off = w.partial_off;
       }
       vec.push_back(make_gemm(5, 2.0f, a));
     }
@@ -351,7 +356,8 @@ class Bert_Model {
 
   // bytes of symmetric memory the model needs from the communicator's data region
   static size_t comm_bytes_needed(const BertInitParam& bp) {
-    const size_t mh = round_up((size_t)bp.max_batch_size * bp.max_seq_len * bp.hidden() * 2, 256);
+    // + kMaxRanks rows: the scattered layout [ws][ceil(M/ws)][H] can exceed M rows by up to ws - 1
+    const size_t mh = round_up(((size_t)bp.max_batch_size * bp.max_seq_len + LIGER_COMM_MAX_RANKS) * bp.hidden() * 2, 256);
     return 3 * mh * (size_t)(bp.workspace_slots > 0 ? bp.workspace_slots : 1);
   }
 
@@ -475,7 +481,7 @@ class Bert_Model {
   void init_workspaces() {
     const int ws = SParam.world_size;
     const size_t M = tokens_max();
-    const size_t mh = round_up(M * H * 2, 256);
+    const size_t mh = round_up((M + LIGER_COMM_MAX_RANKS) * H * 2, 256);
     const int nslots = BertParams.workspace_slots > 0 ? BertParams.workspace_slots : 1;
     uint8_t* sym = nullptr;
     if (ws > 1) {

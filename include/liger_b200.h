@@ -79,7 +79,8 @@ enum liger_epilogue {
   LIGER_EPI_GELU = 1,      /* C = gelu_tanh(acc + bias)                                         */
   LIGER_EPI_GEGLU = 2,     /* C[:, j] = gelu_tanh(gate_j + b) * (value_j + b); C has N/2 columns */
   LIGER_EPI_QKV_SPLIT = 3, /* acc + bias scattered to q / k / v in [B, h, S, D] layout          */
-  LIGER_EPI_RESIDUAL = 4   /* C = acc + bias + residual                                         */
+  LIGER_EPI_RESIDUAL = 4,  /* C = acc + bias + residual                                         */
+  LIGER_EPI_SCATTER = 5    /* row-parallel partial sums stored straight into the owning ranks' memory */
 };
 
 /*
@@ -107,7 +108,14 @@ enum liger_epilogue {
  * {q,k,v}_out[which][((b * heads + head) * seq_len + s) * head_dim + d].  With kv_stride > 0 the K and V
  * outputs are instead rows kv_pos + s of a KV cache laid out [B, heads, kv_stride, head_dim]
  * (prefill fills the cache from position kv_pos = 0, a decode step appends at kv_pos = kv_len).
+ * For LIGER_EPI_SCATTER (the first half of a fused all-reduce: a reduce-scatter done by the GEMM's
+ * own epilogue stores over NVLink, overlapped with its MMAs), row m belongs to rank
+ * owner = m / ceil(M / world_size) and is stored at byte offset scatter_off of the OWNER's
+ * communicator data region, laid out [world_size][ceil(M/world_size)][N], in the slot of the
+ * storing rank.  liger_allreduce_fused(..., one_shot = 3) then finishes the all-reduce from the
+ * local slots.  c, ldc are unused.
  */
+struct liger_comm;
 typedef struct liger_gemm_args {
   const void* a;        /* [M, K] fp16 */
   const void* wt;       /* [N, K] fp16 */
@@ -123,6 +131,8 @@ typedef struct liger_gemm_args {
   int epilogue;
   int seq_len, heads, head_dim; /* LIGER_EPI_QKV_SPLIT only */
   int kv_stride, kv_pos;        /* LIGER_EPI_QKV_SPLIT only: see above; 0, 0 for plain [B, h, S, D] outputs */
+  struct liger_comm* scatter_comm; /* LIGER_EPI_SCATTER only */
+  size_t scatter_off;              /* LIGER_EPI_SCATTER only */
 } liger_gemm_args;
 
 LIGER_API int liger_gemm_fp16(const liger_gemm_args* args, void* stream);
@@ -276,7 +286,9 @@ LIGER_API int liger_comm_timing(liger_comm* comm, int channel, int reset, double
  * preceded and followed by a cross-rank barrier on flag set `channel`, so that a kernel launched
  * after this one on the same stream sees all rows.  With one_shot != 0 every rank instead reduces
  * all rows itself and stores only locally (latency-bound sizes; hidden is then updated for all
- * rows on every rank).  one_shot == 2 turns the call into an all-gather: each rank's own rows of its
+ * rows on every rank).  one_shot == 3: two-shot, but the partials were already scattered to their
+ * owners by GEMMs with LIGER_EPI_SCATTER (partial_off is then the [world_size][rows][N] receive
+ * region) and the reduction reads local memory only.  one_shot == 2 turns the call into an all-gather: each rank's own rows of its
  * partial are taken as they are (no sum over peers) and stored to every rank.
  * Waits on peers are bounded; on timeout the device status word is set.
  * N % 8 == 0, N <= 16384.  row_begin / row_end allow the collective to be issued in slices

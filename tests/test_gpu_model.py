@@ -22,6 +22,10 @@ CASES = {
     "tiny_preln": dict(head_num=16, size_per_head=64, layer_num=2, graph=1, act=0, ffn_inner=4096, causal=1, B=4, S=128),
     # gated FFN, head_dim 128, ragged sequence length
     "preln_geglu": dict(head_num=4, size_per_head=128, layer_num=3, graph=1, act=1, ffn_inner=1024, causal=1, B=3, S=72),
+    # large enough (2 MiB of activations) for the bandwidth path: GEMM epilogues scatter their partial sums to
+    # the owning ranks and the all-reduce finishes from local slots; M not divisible by 128
+    "preln_two_shot": dict(head_num=16, size_per_head=64, layer_num=2, graph=1, act=0, ffn_inner=2048, causal=1, B=4, S=264),
+    "ref_two_shot": dict(head_num=16, size_per_head=64, layer_num=1, graph=0, act=1, ffn_inner=2048, causal=0, B=2, S=520),
     "ref_geglu_causal": dict(head_num=8, size_per_head=64, layer_num=1, graph=0, act=1, ffn_inner=2048, causal=1, B=1, S=200),
 }
 
@@ -146,7 +150,7 @@ def _tp_worker(rank, world, port, case, results):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("case", ["tiny_preln", "ref_gelu", "preln_geglu"])
+@pytest.mark.parametrize("case", ["tiny_preln", "ref_gelu", "preln_geglu", "preln_two_shot", "ref_two_shot"])
 def test_stack_forward_tensor_parallel_2(oracle, case):
     """BASELINE config 1 is the tiny pre-LN stack at TP = 2."""
     import torch
