@@ -47,7 +47,10 @@ struct GemmCfg {
   static constexpr int kBBytes = BN * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kSmemBytes = STAGES * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+  static constexpr int kEpiW = BN < 128 ? BN : 128;             // accumulator columns staged per pass
+  static constexpr int kEpiBytesPerWarp = 32 * kEpiW * 2;       // fp16 staging tile of one epilogue warp
+  static constexpr int kEpiBytes = 4 * kEpiBytesPerWarp;
+  static constexpr int kSmemBytes = STAGES * kStageBytes + kEpiBytes + kBarrierBytes + 1024;  // + alignment slack
   static constexpr int kTmemCols = 2 * BN;
 };
 
@@ -62,62 +65,42 @@ __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
   }
 }
 
-// 32 accumulator columns [col0, col0+32) of one row -> bias / activation -> fp16 stores.
-__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, int row, int col0, const uint32_t (&r)[32]) {
+// 32 accumulator columns [col0, col0+32) of one row -> bias / activation -> 32 fp16 values in o[4].
+__device__ __forceinline__ void epilogue_math(const GemmParams& p, int row, int col0, const uint32_t (&r)[32],
+                                              uint4 (&o)[4]) {
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
     const int col = col0 + g * 8;
-    if (col >= p.n_end) break;
     float v[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]);
-    if (p.bias != nullptr) {
-      float b[8];
-      unpack8(__ldg(reinterpret_cast<const uint4*>(p.bias + col)), b);
+    if (col < p.n_end) {
+      if (p.bias != nullptr) {
+        float b[8];
+        unpack8(__ldg(reinterpret_cast<const uint4*>(p.bias + col)), b);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] += b[i];
-    }
-    if (p.epilogue == LIGER_EPI_GELU) {
+        for (int i = 0; i < 8; ++i) v[i] += b[i];
+      }
+      if (p.epilogue == LIGER_EPI_GELU) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = gelu_tanh(v[i]);
-    } else if (p.epilogue == LIGER_EPI_RESIDUAL) {
-      float b[8];
-      unpack8(__ldg(reinterpret_cast<const uint4*>(p.residual + (size_t)row * p.ldr + col)), b);
+        for (int i = 0; i < 8; ++i) v[i] = gelu_tanh(v[i]);
+      } else if (p.epilogue == LIGER_EPI_RESIDUAL) {
+        float b[8];
+        unpack8(__ldg(reinterpret_cast<const uint4*>(p.residual + (size_t)row * p.ldr + col)), b);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] += b[i];
+        for (int i = 0; i < 8; ++i) v[i] += b[i];
+      }
     }
-    uint4 o;
-    o.x = pack_half2(v[0], v[1]);
-    o.y = pack_half2(v[2], v[3]);
-    o.z = pack_half2(v[4], v[5]);
-    o.w = pack_half2(v[6], v[7]);
-    __half* dst;
-    if (p.epilogue == LIGER_EPI_QKV_SPLIT) {
-      const int hd = p.heads * p.head_dim;
-      const int which = col / hd;
-      const int rem = col - which * hd;
-      const int head = rem / p.head_dim;
-      const int d = rem - head * p.head_dim;
-      const int b = row / p.seq_len;
-      const int s = row - b * p.seq_len;
-      if (which != 0 && p.kv_stride > 0)
-        dst = p.qkv[which] + (((size_t)b * p.heads + head) * p.kv_stride + p.kv_pos + s) * p.head_dim + d;
-      else
-        dst = p.qkv[which] + (((size_t)b * p.heads + head) * p.seq_len + s) * p.head_dim + d;
-    } else if (p.epilogue == LIGER_EPI_SCATTER) {
-      const int owner = row / p.rows_per_rank;
-      const int local_row = p.rank * p.rows_per_rank + (row - owner * p.rows_per_rank);
-      dst = reinterpret_cast<__half*>(p.peer[owner] + p.scatter_off) + (size_t)local_row * p.ldc + col;
-    } else {
-      dst = p.c + (size_t)row * p.ldc + col;
-    }
-    *reinterpret_cast<uint4*>(dst) = o;
+    o[g].x = pack_half2(v[0], v[1]);
+    o[g].y = pack_half2(v[2], v[3]);
+    o[g].z = pack_half2(v[4], v[5]);
+    o[g].w = pack_half2(v[6], v[7]);
   }
 }
 
-// gate chunk + value chunk -> 32 outputs gelu(gate + b) * (value + b) at column out_col0
-__device__ __forceinline__ void epilogue_geglu(const GemmParams& p, int row, int col0, int out_col0,
-                                               const uint32_t (&g)[32], const uint32_t (&u)[32]) {
+// gate chunk (acc columns col0..col0+31) + value chunk (col0+32..col0+63) -> 32 outputs gelu(gate + b) * (value + b)
+__device__ __forceinline__ void epilogue_math_geglu(const GemmParams& p, int col0, const uint32_t (&g)[32],
+                                                    const uint32_t (&u)[32], uint4 (&o)[4]) {
 #pragma unroll
   for (int q = 0; q < 4; ++q) {
     float gv[8], uv[8];
@@ -126,7 +109,7 @@ __device__ __forceinline__ void epilogue_geglu(const GemmParams& p, int row, int
       gv[i] = __uint_as_float(g[q * 8 + i]);
       uv[i] = __uint_as_float(u[q * 8 + i]);
     }
-    if (p.bias != nullptr) {
+    if (p.bias != nullptr && col0 < p.n_end) {
       float b[8];
       unpack8(__ldg(reinterpret_cast<const uint4*>(p.bias + col0 + q * 8)), b);
 #pragma unroll
@@ -137,12 +120,59 @@ __device__ __forceinline__ void epilogue_geglu(const GemmParams& p, int row, int
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) gv[i] = gelu_tanh(gv[i]) * uv[i];
-    uint4 o;
-    o.x = pack_half2(gv[0], gv[1]);
-    o.y = pack_half2(gv[2], gv[3]);
-    o.z = pack_half2(gv[4], gv[5]);
-    o.w = pack_half2(gv[6], gv[7]);
-    *reinterpret_cast<uint4*>(p.c + (size_t)row * p.ldc + out_col0 + q * 8) = o;
+    o[q].x = pack_half2(gv[0], gv[1]);
+    o[q].y = pack_half2(gv[2], gv[3]);
+    o[q].z = pack_half2(gv[4], gv[5]);
+    o[q].w = pack_half2(gv[6], gv[7]);
+  }
+}
+
+// Where 8 consecutive outputs of (row, out_col) go.  out_col is in output-column space (for GeGLU
+// already halved).
+__device__ __forceinline__ __half* epilogue_dst(const GemmParams& p, int row, int out_col) {
+  if (p.epilogue == LIGER_EPI_QKV_SPLIT) {
+    const int hd = p.heads * p.head_dim;
+    const int which = out_col / hd;
+    const int rem = out_col - which * hd;
+    const int head = rem / p.head_dim;
+    const int d = rem - head * p.head_dim;
+    const int b = row / p.seq_len;
+    const int s = row - b * p.seq_len;
+    __half* base = which == 0 ? p.qkv[0] : which == 1 ? p.qkv[1] : p.qkv[2];
+    if (which != 0 && p.kv_stride > 0)
+      return base + (((size_t)b * p.heads + head) * p.kv_stride + p.kv_pos + s) * p.head_dim + d;
+    return base + (((size_t)b * p.heads + head) * p.seq_len + s) * p.head_dim + d;
+  }
+  if (p.epilogue == LIGER_EPI_SCATTER) {
+    const int owner = row / p.rows_per_rank;
+    const int local_row = p.rank * p.rows_per_rank + (row - owner * p.rows_per_rank);
+    return reinterpret_cast<__half*>(p.peer[owner] + p.scatter_off) + (size_t)local_row * p.ldc + out_col;
+  }
+  return p.c + (size_t)row * p.ldc + out_col;
+}
+
+// Per-warp staging tile in shared memory: 32 rows x W output columns (fp16), 16-byte chunks XOR-swizzled
+// by row so that both the row-per-thread writes and the row-contiguous reads are conflict-light.
+template <int W>
+__device__ __forceinline__ uint4* stage_slot(uint8_t* stage, int r, int chunk) {
+  constexpr int NCH = W / 8;                       // 16-byte chunks per row
+  constexpr int MASK = (NCH < 8 ? NCH : 8) - 1;
+  return reinterpret_cast<uint4*>(stage + (size_t)r * (W * 2) + (size_t)((chunk ^ (r & MASK)) * 16));
+}
+
+// Write the staged [32 x W] tile out with row-contiguous 16-byte stores: a warp instruction covers
+// 32/NCH rows of W*2 contiguous bytes each (256 B for W = 128), which is what both HBM sectors and
+// NVLink write packets want -- row-per-thread stores would issue 32 separate 16-byte writes.
+template <int W>
+__device__ __forceinline__ void stage_writeout(const GemmParams& p, uint8_t* stage, int row0, int out_col0, int out_end,
+                                               int lane) {
+  constexpr int NCH = W / 8;
+#pragma unroll 4
+  for (int i = 0; i < NCH; ++i) {
+    const int idx = i * 32 + lane;
+    const int r = idx / NCH, ch = idx % NCH;
+    const int row = row0 + r, col = out_col0 + ch * 8;
+    if (row < p.m && col < out_end) *reinterpret_cast<uint4*>(epilogue_dst(p, row, col)) = *stage_slot<W>(stage, r, ch);
   }
 }
 
@@ -154,7 +184,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   using Cfg = GemmCfg<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::kStageBytes);
+  uint8_t* epi_stage = smem + STAGES * Cfg::kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_stage + Cfg::kEpiBytes);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tmem_full = empty_bar + STAGES;
   uint64_t* tmem_empty = tmem_full + 2;
@@ -255,29 +286,50 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const int n0 = p.n_begin + (t / p.tiles_m) * BN;
       if (!mbar_wait_bounded(&tmem_full[acc], acc_phase, abort_flag)) break;
       tc_fence_after();
-      const int row = m0 + quad * 32 + lane;
+      const int row0 = m0 + quad * 32;
+      const int row = row0 + lane;
       const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
-      if (p.epilogue == LIGER_EPI_GEGLU) {
+      uint8_t* stage = epi_stage + (warp - 2) * Cfg::kEpiBytesPerWarp;
+      constexpr int W = Cfg::kEpiW;
 #pragma unroll 1
-        for (int c = 0; c < BN / 64; ++c) {
-          const int col0 = n0 + c * 64;
-          if (col0 >= p.n_end) break;
-          uint32_t g[32], u[32];
-          tmem_ld_32x32(taddr + c * 64, g);
-          tmem_ld_32x32(taddr + c * 64 + 32, u);
-          tmem_ld_wait();
-          if (row < p.m) epilogue_geglu(p, row, col0, col0 >> 1, g, u);
-        }
-      } else {
+      for (int pass = 0; pass < BN / W; ++pass) {
+        const int pcol0 = n0 + pass * W;          // first accumulator column of this pass
+        if (pcol0 >= p.n_end) break;
+        if (p.epilogue == LIGER_EPI_GEGLU) {
+          if constexpr (W >= 64) {
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          const int col0 = n0 + c * 32;
-          if (col0 >= p.n_end) break;
-          uint32_t r[32];
-          tmem_ld_32x32(taddr + c * 32, r);
-          tmem_ld_wait();
-          if (row < p.m) epilogue_chunk(p, row, col0, r);
+            for (int c = 0; c < W / 64; ++c) {
+              const int col0 = pcol0 + c * 64;
+              if (col0 >= p.n_end) break;
+              uint32_t g[32], u[32];
+              tmem_ld_32x32(taddr + pass * W + c * 64, g);
+              tmem_ld_32x32(taddr + pass * W + c * 64 + 32, u);
+              tmem_ld_wait();
+              uint4 o[4];
+              epilogue_math_geglu(p, col0, g, u, o);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) *stage_slot<W / 2>(stage, lane, c * 4 + j) = o[j];
+            }
+            __syncwarp();
+            stage_writeout<W / 2>(p, stage, row0, pcol0 >> 1, p.n_end >> 1, lane);
+          }
+        } else {
+#pragma unroll 1
+          for (int c = 0; c < W / 32; ++c) {
+            const int col0 = pcol0 + c * 32;
+            if (col0 >= p.n_end) break;
+            uint32_t r[32];
+            tmem_ld_32x32(taddr + pass * W + c * 32, r);
+            tmem_ld_wait();
+            uint4 o[4];
+            epilogue_math(p, row < p.m ? row : 0, col0, r, o);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) *stage_slot<W>(stage, lane, c * 4 + j) = o[j];
+          }
+          __syncwarp();
+          stage_writeout<W>(p, stage, row0, pcol0, p.n_end, lane);
         }
+        __syncwarp();   // the staging tile is reused by the next pass
       }
       tc_fence_before();
       __syncwarp();
