@@ -12,6 +12,7 @@
 // are handed out by the host per launch.  Every wait is bounded (common.cuh).
 #include <unistd.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -419,7 +420,15 @@ extern "C" int liger_allreduce_fused(liger_comm* c, int channel, size_t partial_
     if (hi < lo) hi = lo;
   }
   int grid = hi - lo;
-  const int cap = dev->sm_count * 4;
+  // The collective is bandwidth bound (NVLink for the stores to peers, HBM for the local reads); a
+  // fraction of the SMs saturates both, and every CTA beyond that only takes registers and issue
+  // slots away from the GEMMs and attention kernels of other requests running next to it.
+  static int max_ctas = -1;
+  if (max_ctas < 0) {
+    const char* e = getenv("LIGER_AR_MAX_CTAS");
+    max_ctas = (e && atoi(e) > 0) ? atoi(e) : dev->sm_count * 4;
+  }
+  const int cap = max_ctas;
   if (grid > cap) grid = cap;
   if (grid < 1) grid = 1;
   const uint32_t e_in = ++c->epoch[channel];

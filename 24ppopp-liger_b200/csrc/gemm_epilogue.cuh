@@ -1,0 +1,203 @@
+// Shared by the 1-CTA and 2-CTA tcgen05 GEMM kernels: launch parameters and the epilogue (TMEM ->
+// registers -> bias / activation -> shared-memory staging -> row-contiguous 16-byte stores).
+#pragma once
+#include "comm_internal.h"
+#include "runtime.h"
+
+namespace liger {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int kGemmThreads = 192;
+
+struct GemmParams {
+  __half* c;
+  const __half* bias;
+  const __half* residual;
+  __half* qkv[3];
+  int m, n_begin, n_end;
+  int ldc, ldr;
+  int epilogue;
+  int seq_len, heads, head_dim;
+  int kv_stride, kv_pos;
+  int tiles_m, tiles_n, kblocks;
+  // LIGER_EPI_SCATTER: row r goes to rank r / rows_per_rank, into that rank's receive slot for this rank
+  uint8_t* peer[kMaxRanks];
+  size_t scatter_off;
+  int rank, rows_per_rank;
+  DeviceStatus* status;
+};
+
+// ---- epilogue helpers -------------------------------------------------------------------------
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __half22float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+
+// 32 accumulator columns [col0, col0+32) of one row -> bias / activation -> 32 fp16 values in o[4].
+__device__ __forceinline__ void epilogue_math(const GemmParams& p, int row, int col0, const uint32_t (&r)[32],
+                                              uint4 (&o)[4]) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const int col = col0 + g * 8;
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]);
+    if (col < p.n_end) {
+      if (p.bias != nullptr) {
+        float b[8];
+        unpack8(__ldg(reinterpret_cast<const uint4*>(p.bias + col)), b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] += b[i];
+      }
+      if (p.epilogue == LIGER_EPI_GELU) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = gelu_tanh(v[i]);
+      } else if (p.epilogue == LIGER_EPI_RESIDUAL) {
+        float b[8];
+        unpack8(__ldg(reinterpret_cast<const uint4*>(p.residual + (size_t)row * p.ldr + col)), b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] += b[i];
+      }
+    }
+    o[g].x = pack_half2(v[0], v[1]);
+    o[g].y = pack_half2(v[2], v[3]);
+    o[g].z = pack_half2(v[4], v[5]);
+    o[g].w = pack_half2(v[6], v[7]);
+  }
+}
+
+// gate chunk (acc columns col0..col0+31) + value chunk (col0+32..col0+63) -> 32 outputs gelu(gate + b) * (value + b)
+__device__ __forceinline__ void epilogue_math_geglu(const GemmParams& p, int col0, const uint32_t (&g)[32],
+                                                    const uint32_t (&u)[32], uint4 (&o)[4]) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    float gv[8], uv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      gv[i] = __uint_as_float(g[q * 8 + i]);
+      uv[i] = __uint_as_float(u[q * 8 + i]);
+    }
+    if (p.bias != nullptr && col0 < p.n_end) {
+      float b[8];
+      unpack8(__ldg(reinterpret_cast<const uint4*>(p.bias + col0 + q * 8)), b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) gv[i] += b[i];
+      unpack8(__ldg(reinterpret_cast<const uint4*>(p.bias + col0 + 32 + q * 8)), b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) uv[i] += b[i];
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) gv[i] = gelu_tanh(gv[i]) * uv[i];
+    o[q].x = pack_half2(gv[0], gv[1]);
+    o[q].y = pack_half2(gv[2], gv[3]);
+    o[q].z = pack_half2(gv[4], gv[5]);
+    o[q].w = pack_half2(gv[6], gv[7]);
+  }
+}
+
+// Where 8 consecutive outputs of (row, out_col) go.  out_col is in output-column space (for GeGLU
+// already halved).
+__device__ __forceinline__ __half* epilogue_dst(const GemmParams& p, int row, int out_col) {
+  if (p.epilogue == LIGER_EPI_QKV_SPLIT) {
+    const int hd = p.heads * p.head_dim;
+    const int which = out_col / hd;
+    const int rem = out_col - which * hd;
+    const int head = rem / p.head_dim;
+    const int d = rem - head * p.head_dim;
+    const int b = row / p.seq_len;
+    const int s = row - b * p.seq_len;
+    __half* base = which == 0 ? p.qkv[0] : which == 1 ? p.qkv[1] : p.qkv[2];
+    if (which != 0 && p.kv_stride > 0)
+      return base + (((size_t)b * p.heads + head) * p.kv_stride + p.kv_pos + s) * p.head_dim + d;
+    return base + (((size_t)b * p.heads + head) * p.seq_len + s) * p.head_dim + d;
+  }
+  if (p.epilogue == LIGER_EPI_SCATTER) {
+    const int owner = row / p.rows_per_rank;
+    const int local_row = p.rank * p.rows_per_rank + (row - owner * p.rows_per_rank);
+    return reinterpret_cast<__half*>(p.peer[owner] + p.scatter_off) + (size_t)local_row * p.ldc + out_col;
+  }
+  return p.c + (size_t)row * p.ldc + out_col;
+}
+
+// Per-warp staging tile in shared memory: 32 rows x W output columns (fp16), 16-byte chunks XOR-swizzled
+// by row so that both the row-per-thread writes and the row-contiguous reads are conflict-light.
+template <int W>
+__device__ __forceinline__ uint4* stage_slot(uint8_t* stage, int r, int chunk) {
+  constexpr int NCH = W / 8;                       // 16-byte chunks per row
+  constexpr int MASK = (NCH < 8 ? NCH : 8) - 1;
+  return reinterpret_cast<uint4*>(stage + (size_t)r * (W * 2) + (size_t)((chunk ^ (r & MASK)) * 16));
+}
+
+// Write the staged [32 x W] tile out with row-contiguous 16-byte stores: a warp instruction covers
+// 32/NCH rows of W*2 contiguous bytes each (256 B for W = 128), which is what both HBM sectors and
+// NVLink write packets want -- row-per-thread stores would issue 32 separate 16-byte writes.
+template <int W>
+__device__ __forceinline__ void stage_writeout(const GemmParams& p, uint8_t* stage, int row0, int out_col0, int out_end,
+                                               int lane) {
+  constexpr int NCH = W / 8;
+#pragma unroll 4
+  for (int i = 0; i < NCH; ++i) {
+    const int idx = i * 32 + lane;
+    const int r = idx / NCH, ch = idx % NCH;
+    const int row = row0 + r, col = out_col0 + ch * 8;
+    if (row < p.m && col < out_end) *reinterpret_cast<uint4*>(epilogue_dst(p, row, col)) = *stage_slot<W>(stage, r, ch);
+  }
+}
+
+
+// Epilogue of one accumulator tile for one warp: TMEM lanes [taddr.lane, +32) x BN columns -> rows
+// [row0, row0+32), accumulator columns [n0, n0+BN).  `stage` is this warp's staging tile.
+template <int BN>
+__device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t taddr, uint8_t* stage, int row0, int n0,
+                                              int lane) {
+  constexpr int W = BN < 128 ? BN : 128;
+  const int row = row0 + lane;
+#pragma unroll 1
+  for (int pass = 0; pass < BN / W; ++pass) {
+    const int pcol0 = n0 + pass * W;  // first accumulator column of this pass
+    if (pcol0 >= p.n_end) break;
+    if (p.epilogue == LIGER_EPI_GEGLU) {
+      if constexpr (W >= 64) {
+#pragma unroll 1
+        for (int c = 0; c < W / 64; ++c) {
+          const int col0 = pcol0 + c * 64;
+          if (col0 >= p.n_end) break;
+          uint32_t g[32], u[32];
+          tmem_ld_32x32(taddr + pass * W + c * 64, g);
+          tmem_ld_32x32(taddr + pass * W + c * 64 + 32, u);
+          tmem_ld_wait();
+          uint4 o[4];
+          epilogue_math_geglu(p, col0, g, u, o);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) *stage_slot<W / 2>(stage, lane, c * 4 + j) = o[j];
+        }
+        __syncwarp();
+        stage_writeout<W / 2>(p, stage, row0, pcol0 >> 1, p.n_end >> 1, lane);
+      }
+    } else {
+#pragma unroll 1
+      for (int c = 0; c < W / 32; ++c) {
+        const int col0 = pcol0 + c * 32;
+        if (col0 >= p.n_end) break;
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + pass * W + c * 32, r);
+        tmem_ld_wait();
+        uint4 o[4];
+        epilogue_math(p, row < p.m ? row : 0, col0, r, o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) *stage_slot<W>(stage, lane, c * 4 + j) = o[j];
+      }
+      __syncwarp();
+      stage_writeout<W>(p, stage, row0, pcol0, p.n_end, lane);
+    }
+    __syncwarp();  // the staging tile is reused by the next pass
+  }
+}
+
+}  // namespace liger

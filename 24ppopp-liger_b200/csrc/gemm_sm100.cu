@@ -14,32 +14,11 @@
 //             scatter in registers, 16-byte fp16 stores; then `tmem_empty` lets the MMA warp
 //             reuse the accumulator, so the epilogue of tile i overlaps the MMAs of tile i+1.
 // All waits are bounded (common.cuh); a timeout sets the sticky status word and the CTA unwinds.
-#include "comm_internal.h"
-#include "runtime.h"
+#include <cstdlib>
+
+#include "gemm_epilogue.cuh"
 
 namespace liger {
-
-constexpr int BM = 128;
-constexpr int BK = 64;
-constexpr int kGemmThreads = 192;
-
-struct GemmParams {
-  __half* c;
-  const __half* bias;
-  const __half* residual;
-  __half* qkv[3];
-  int m, n_begin, n_end;
-  int ldc, ldr;
-  int epilogue;
-  int seq_len, heads, head_dim;
-  int kv_stride, kv_pos;
-  int tiles_m, tiles_n, kblocks;
-  // LIGER_EPI_SCATTER: row r goes to rank r / rows_per_rank, into that rank's receive slot for this rank
-  uint8_t* peer[kMaxRanks];
-  size_t scatter_off;
-  int rank, rows_per_rank;
-  DeviceStatus* status;
-};
 
 template <int BN, int STAGES>
 struct GemmCfg {
@@ -53,128 +32,6 @@ struct GemmCfg {
   static constexpr int kSmemBytes = STAGES * kStageBytes + kEpiBytes + kBarrierBytes + 1024;  // + alignment slack
   static constexpr int kTmemCols = 2 * BN;
 };
-
-// ---- epilogue helpers -------------------------------------------------------------------------
-__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
-  const __half2* h = reinterpret_cast<const __half2*>(&u);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 t = __half22float2(h[i]);
-    f[2 * i] = t.x;
-    f[2 * i + 1] = t.y;
-  }
-}
-
-// 32 accumulator columns [col0, col0+32) of one row -> bias / activation -> 32 fp16 values in o[4].
-__device__ __forceinline__ void epilogue_math(const GemmParams& p, int row, int col0, const uint32_t (&r)[32],
-                                              uint4 (&o)[4]) {
-#pragma unroll
-  for (int g = 0; g < 4; ++g) {
-    const int col = col0 + g * 8;
-    float v[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]);
-    if (col < p.n_end) {
-      if (p.bias != nullptr) {
-        float b[8];
-        unpack8(__ldg(reinterpret_cast<const uint4*>(p.bias + col)), b);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] += b[i];
-      }
-      if (p.epilogue == LIGER_EPI_GELU) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = gelu_tanh(v[i]);
-      } else if (p.epilogue == LIGER_EPI_RESIDUAL) {
-        float b[8];
-        unpack8(__ldg(reinterpret_cast<const uint4*>(p.residual + (size_t)row * p.ldr + col)), b);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] += b[i];
-      }
-    }
-    o[g].x = pack_half2(v[0], v[1]);
-    o[g].y = pack_half2(v[2], v[3]);
-    o[g].z = pack_half2(v[4], v[5]);
-    o[g].w = pack_half2(v[6], v[7]);
-  }
-}
-
-// gate chunk (acc columns col0..col0+31) + value chunk (col0+32..col0+63) -> 32 outputs gelu(gate + b) * (value + b)
-__device__ __forceinline__ void epilogue_math_geglu(const GemmParams& p, int col0, const uint32_t (&g)[32],
-                                                    const uint32_t (&u)[32], uint4 (&o)[4]) {
-#pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    float gv[8], uv[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      gv[i] = __uint_as_float(g[q * 8 + i]);
-      uv[i] = __uint_as_float(u[q * 8 + i]);
-    }
-    if (p.bias != nullptr && col0 < p.n_end) {
-      float b[8];
-      unpack8(__ldg(reinterpret_cast<const uint4*>(p.bias + col0 + q * 8)), b);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) gv[i] += b[i];
-      unpack8(__ldg(reinterpret_cast<const uint4*>(p.bias + col0 + 32 + q * 8)), b);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) uv[i] += b[i];
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) gv[i] = gelu_tanh(gv[i]) * uv[i];
-    o[q].x = pack_half2(gv[0], gv[1]);
-    o[q].y = pack_half2(gv[2], gv[3]);
-    o[q].z = pack_half2(gv[4], gv[5]);
-    o[q].w = pack_half2(gv[6], gv[7]);
-  }
-}
-
-// Where 8 consecutive outputs of (row, out_col) go.  out_col is in output-column space (for GeGLU
-// already halved).
-__device__ __forceinline__ __half* epilogue_dst(const GemmParams& p, int row, int out_col) {
-  if (p.epilogue == LIGER_EPI_QKV_SPLIT) {
-    const int hd = p.heads * p.head_dim;
-    const int which = out_col / hd;
-    const int rem = out_col - which * hd;
-    const int head = rem / p.head_dim;
-    const int d = rem - head * p.head_dim;
-    const int b = row / p.seq_len;
-    const int s = row - b * p.seq_len;
-    __half* base = which == 0 ? p.qkv[0] : which == 1 ? p.qkv[1] : p.qkv[2];
-    if (which != 0 && p.kv_stride > 0)
-      return base + (((size_t)b * p.heads + head) * p.kv_stride + p.kv_pos + s) * p.head_dim + d;
-    return base + (((size_t)b * p.heads + head) * p.seq_len + s) * p.head_dim + d;
-  }
-  if (p.epilogue == LIGER_EPI_SCATTER) {
-    const int owner = row / p.rows_per_rank;
-    const int local_row = p.rank * p.rows_per_rank + (row - owner * p.rows_per_rank);
-    return reinterpret_cast<__half*>(p.peer[owner] + p.scatter_off) + (size_t)local_row * p.ldc + out_col;
-  }
-  return p.c + (size_t)row * p.ldc + out_col;
-}
-
-// Per-warp staging tile in shared memory: 32 rows x W output columns (fp16), 16-byte chunks XOR-swizzled
-// by row so that both the row-per-thread writes and the row-contiguous reads are conflict-light.
-template <int W>
-__device__ __forceinline__ uint4* stage_slot(uint8_t* stage, int r, int chunk) {
-  constexpr int NCH = W / 8;                       // 16-byte chunks per row
-  constexpr int MASK = (NCH < 8 ? NCH : 8) - 1;
-  return reinterpret_cast<uint4*>(stage + (size_t)r * (W * 2) + (size_t)((chunk ^ (r & MASK)) * 16));
-}
-
-// Write the staged [32 x W] tile out with row-contiguous 16-byte stores: a warp instruction covers
-// 32/NCH rows of W*2 contiguous bytes each (256 B for W = 128), which is what both HBM sectors and
-// NVLink write packets want -- row-per-thread stores would issue 32 separate 16-byte writes.
-template <int W>
-__device__ __forceinline__ void stage_writeout(const GemmParams& p, uint8_t* stage, int row0, int out_col0, int out_end,
-                                               int lane) {
-  constexpr int NCH = W / 8;
-#pragma unroll 4
-  for (int i = 0; i < NCH; ++i) {
-    const int idx = i * 32 + lane;
-    const int r = idx / NCH, ch = idx % NCH;
-    const int row = row0 + r, col = out_col0 + ch * 8;
-    if (row < p.m && col < out_end) *reinterpret_cast<uint4*>(epilogue_dst(p, row, col)) = *stage_slot<W>(stage, r, ch);
-  }
-}
 
 // ---- the kernel -------------------------------------------------------------------------------
 template <int BN, int STAGES>
@@ -286,51 +143,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const int n0 = p.n_begin + (t / p.tiles_m) * BN;
       if (!mbar_wait_bounded(&tmem_full[acc], acc_phase, abort_flag)) break;
       tc_fence_after();
-      const int row0 = m0 + quad * 32;
-      const int row = row0 + lane;
-      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
-      uint8_t* stage = epi_stage + (warp - 2) * Cfg::kEpiBytesPerWarp;
-      constexpr int W = Cfg::kEpiW;
-#pragma unroll 1
-      for (int pass = 0; pass < BN / W; ++pass) {
-        const int pcol0 = n0 + pass * W;          // first accumulator column of this pass
-        if (pcol0 >= p.n_end) break;
-        if (p.epilogue == LIGER_EPI_GEGLU) {
-          if constexpr (W >= 64) {
-#pragma unroll 1
-            for (int c = 0; c < W / 64; ++c) {
-              const int col0 = pcol0 + c * 64;
-              if (col0 >= p.n_end) break;
-              uint32_t g[32], u[32];
-              tmem_ld_32x32(taddr + pass * W + c * 64, g);
-              tmem_ld_32x32(taddr + pass * W + c * 64 + 32, u);
-              tmem_ld_wait();
-              uint4 o[4];
-              epilogue_math_geglu(p, col0, g, u, o);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) *stage_slot<W / 2>(stage, lane, c * 4 + j) = o[j];
-            }
-            __syncwarp();
-            stage_writeout<W / 2>(p, stage, row0, pcol0 >> 1, p.n_end >> 1, lane);
-          }
-        } else {
-#pragma unroll 1
-          for (int c = 0; c < W / 32; ++c) {
-            const int col0 = pcol0 + c * 32;
-            if (col0 >= p.n_end) break;
-            uint32_t r[32];
-            tmem_ld_32x32(taddr + pass * W + c * 32, r);
-            tmem_ld_wait();
-            uint4 o[4];
-            epilogue_math(p, row < p.m ? row : 0, col0, r, o);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) *stage_slot<W>(stage, lane, c * 4 + j) = o[j];
-          }
-          __syncwarp();
-          stage_writeout<W>(p, stage, row0, pcol0, p.n_end, lane);
-        }
-        __syncwarp();   // the staging tile is reused by the next pass
-      }
+      epilogue_tile<BN>(p, tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16),
+                        epi_stage + (warp - 2) * Cfg::kEpiBytesPerWarp, m0 + quad * 32, n0, lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
@@ -369,6 +183,18 @@ static int launch_gemm(const liger_gemm_args& a, const GemmParams& p0, int sm_co
   const int grid = tiles < sm_count ? tiles : sm_count;
   gemm_tcgen05_kernel<BN, STAGES><<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(tm_a, tm_b, p);
   return check_launch("gemm_tcgen05_kernel");
+}
+
+int launch_gemm_2cta(const liger_gemm_args& a, const GemmParams& p0, int sm_count, cudaStream_t stream);
+
+// 0 = choose automatically, 1 = 1-CTA kernel only, 2 = 2-CTA kernel whenever the shape allows
+static int g_gemm_variant = -1;
+static int gemm_variant() {
+  if (g_gemm_variant < 0) {
+    const char* e = getenv("LIGER_GEMM_VARIANT");
+    g_gemm_variant = e ? atoi(e) : 0;
+  }
+  return g_gemm_variant;
 }
 
 }  // namespace liger
@@ -454,6 +280,13 @@ extern "C" int liger_gemm_fp16(const liger_gemm_args* args, void* stream) {
     if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_bn = bn; }
   }
   cudaStream_t s = (cudaStream_t)stream;
+  // 2-CTA 256x256 tiles when there is at least one full wave of them (one tile per SM pair)
+  const long tiles2 = (long)((a.m + 255) / 256) * ((span + 255) / 256);
+  const int variant = gemm_variant();
+  if (variant != 1 && a.m >= 256 && (variant == 2 || tiles2 >= dev->sm_count / 2)) {
+    const int rc2 = launch_gemm_2cta(a, p, dev->sm_count, s);
+    if (rc2 != LIGER_ERR_UNSUPPORTED) return rc2;
+  }
   switch (best_bn) {
     case 256: return launch_gemm<256, 4>(a, p, dev->sm_count, s);
     case 128: return launch_gemm<128, 6>(a, p, dev->sm_count, s);

@@ -26,8 +26,14 @@ struct liger_model {
   std::vector<cudaStream_t> aux_streams;
   cudaEvent_t ev_fork = nullptr;
   std::vector<cudaEvent_t> ev_join;
+  std::vector<cudaEvent_t> ev_chain;  // ring of events ordering the compute segments across streams
+  size_t ev_chain_next = 0;
   std::vector<cudaEvent_t> ev_pool;                      // reusable events
   std::vector<std::pair<int, std::pair<cudaEvent_t, cudaEvent_t>>> ev_rec;  // (name, (before, after))
+  bool timeline = false;  // record per-kernel events in interleaved passes too (diagnostics)
+  struct TimelineRec { int name, stream; cudaEvent_t e0, e1; };
+  std::vector<TimelineRec> tl_rec;
+  cudaEvent_t tl_base = nullptr;
   cudaEvent_t get_event() {
     if (!ev_pool.empty()) { cudaEvent_t e = ev_pool.back(); ev_pool.pop_back(); return e; }
     cudaEvent_t e = nullptr;
@@ -173,7 +179,23 @@ static int forward_interleaved(liger_model* m, const void* input, void* output, 
     vecs.push_back(m->model->forward((const half_t*)input + i * rows * H, (half_t*)output + i * rows * H, sub, seq_len,
                                      slot0 + i));
   LIGER_CUDA_TRY(cudaEventRecord(m->ev_fork, caller));
+  if (m->timeline) {
+    if (!m->tl_base) cudaEventCreate(&m->tl_base);
+    m->tl_rec.clear();
+    cudaEventRecord(m->tl_base, caller);
+  }
   for (int i = 0; i < mb; ++i) LIGER_CUDA_TRY(cudaStreamWaitEvent(m->aux_streams[i], m->ev_fork, 0));
+  // Compute segments of all micro-requests are chained through events in issue order (a0, a1, b0,
+  // b1, ...): they could not share the SMs anyway, and the chain is what staggers the streams so that
+  // the all-reduce that follows a0 runs under a1, the one after a1 under b0, and so on.  Without it
+  // the streams drift into lockstep and all-reduces only overlap each other.
+  while (m->ev_chain.size() < 64) {
+    cudaEvent_t e = nullptr;
+    LIGER_CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    m->ev_chain.push_back(e);
+  }
+  cudaEvent_t last_compute = nullptr;
+  int last_compute_stream = -1;
   std::vector<size_t> cur(mb, 0);
   int n = 0;
   bool more = true;
@@ -187,11 +209,22 @@ static int forward_interleaved(liger_model* m, const void* input, void* output, 
       dp.index = i;
       // one segment: a maximal run of kernels of the same class (communication / not)
       const bool comm = v[cur[i]].type == COMMUNICATION;
+      static const bool stagger = !(getenv("LIGER_STAGGER") && atoi(getenv("LIGER_STAGGER")) == 0);
+      if (stagger && !comm && last_compute != nullptr && last_compute_stream != i)
+        LIGER_CUDA_TRY(cudaStreamWaitEvent(m->aux_streams[i], last_compute, 0));
       while (cur[i] < v.size() && (v[cur[i]].type == COMMUNICATION) == comm) {
+        cudaEvent_t e0 = nullptr, e1 = nullptr;
+        if (m->timeline) { cudaEventCreate(&e0); cudaEventCreate(&e1); cudaEventRecord(e0, m->aux_streams[i]); }
         const int rc = v[cur[i]].callback(dp);
+        if (m->timeline) { cudaEventRecord(e1, m->aux_streams[i]); m->tl_rec.push_back({v[cur[i]].name, i, e0, e1}); }
         if (rc != LIGER_OK) return rc;
         ++cur[i];
         ++n;
+      }
+      if (!comm) {
+        last_compute = m->ev_chain[m->ev_chain_next++ % m->ev_chain.size()];
+        last_compute_stream = i;
+        LIGER_CUDA_TRY(cudaEventRecord(last_compute, m->aux_streams[i]));
       }
       if (cur[i] < v.size()) more = true;
     }
@@ -220,6 +253,25 @@ extern "C" int liger_model_forward(liger_model* m, const void* input, void* outp
   } catch (const std::exception& e) {
     return liger::set_error(LIGER_ERR_INVALID, "model_forward: %s", e.what());
   }
+}
+
+extern "C" int liger_model_timeline(liger_model* m, int enable, int capacity, int* names, int* streams, double* start_ms,
+                                    double* end_ms) {
+  if (!m) return liger::set_error(LIGER_ERR_INVALID, "model_timeline: null model");
+  int n = 0;
+  if (names && streams && start_ms && end_ms) {
+    LIGER_CUDA_TRY(cudaDeviceSynchronize());
+    for (auto& r : m->tl_rec) {
+      if (n >= capacity) break;
+      float a = 0.0f, b = 0.0f;
+      cudaEventElapsedTime(&a, m->tl_base, r.e0);
+      cudaEventElapsedTime(&b, m->tl_base, r.e1);
+      names[n] = r.name; streams[n] = r.stream; start_ms[n] = a; end_ms[n] = b;
+      ++n;
+    }
+  }
+  m->timeline = enable != 0;
+  return n;
 }
 
 extern "C" int liger_model_set_micro_batches(liger_model* m, int micro_batches) {

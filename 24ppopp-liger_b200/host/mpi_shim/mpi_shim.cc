@@ -9,6 +9,7 @@
 
 #include <fcntl.h>
 #include <sched.h>
+#include <signal.h>
 #include <sys/mman.h>
 #include <sys/stat.h>
 #include <time.h>
@@ -18,6 +19,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstdlib>
+#include <cerrno>
 #include <cstring>
 #include <string>
 
@@ -28,6 +30,7 @@ constexpr size_t kMailbox = 65536;
 
 struct Segment {
   std::atomic<uint32_t> magic;
+  std::atomic<int> creator_pid;  // rank 0 of the job that created the segment
   std::atomic<int> attached;
   std::atomic<int> bar_count;
   std::atomic<int> bar_gen;
@@ -102,42 +105,64 @@ int MPI_Init_thread(int*, char***, int required, int* provided) {
   if (job && *job) snprintf(buf, sizeof(buf), "/liger_mpi_%s", job);
   else snprintf(buf, sizeof(buf), "/liger_mpi_ppid%d", (int)getppid());
   g_name = buf;
-  int fd = -1;
-  if (g_rank == 0) {
-    shm_unlink(g_name.c_str());
-    fd = shm_open(g_name.c_str(), O_CREAT | O_EXCL | O_RDWR, 0600);
-    if (fd < 0 || ftruncate(fd, sizeof(Segment)) != 0) {
-      perror("[liger mpi shim] shm_open/ftruncate");
+  // Rank 0 always replaces whatever segment of that name a previous (possibly crashed) job left
+  // behind.  The other ranks may open the name before rank 0 got that far, so they verify what they
+  // mapped: the creator must still be alive and the attach count must not exceed the world size;
+  // otherwise they let go and look again.
+  const double t_begin = now_s();
+  for (;;) {
+    int fd = -1;
+    if (g_rank == 0) {
+      shm_unlink(g_name.c_str());
+      fd = shm_open(g_name.c_str(), O_CREAT | O_EXCL | O_RDWR, 0600);
+      if (fd < 0 || ftruncate(fd, sizeof(Segment)) != 0) {
+        perror("[liger mpi shim] shm_open/ftruncate");
+        return MPI_ERR_OTHER;
+      }
+    } else {
+      while ((fd = shm_open(g_name.c_str(), O_RDWR, 0600)) < 0) {
+        usleep(1000);
+        if (now_s() - t_begin > g_timeout_s) { fprintf(stderr, "[liger mpi shim] rank %d: no segment %s\n", g_rank, buf); return MPI_ERR_OTHER; }
+      }
+      struct stat st;
+      while (fstat(fd, &st) == 0 && (size_t)st.st_size < sizeof(Segment)) {
+        usleep(1000);
+        if (now_s() - t_begin > g_timeout_s) return MPI_ERR_OTHER;
+      }
+    }
+    void* p = mmap(nullptr, sizeof(Segment), PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+    close(fd);
+    if (p == MAP_FAILED) { perror("[liger mpi shim] mmap"); return MPI_ERR_OTHER; }
+    g_seg = (Segment*)p;
+    if (g_rank == 0) {
+      g_seg->creator_pid.store((int)getpid());
+      g_seg->attached.store(1);
+      g_seg->bar_count.store(0);
+      g_seg->bar_gen.store(0);
+      g_seg->bc_seq.store(0);
+      g_seg->bc_acks.store(g_size - 1);
+      g_seg->magic.store(kMagic, std::memory_order_release);
+      break;
+    }
+    bool fresh = false;
+    const double t_map = now_s();
+    while (now_s() - t_map < 0.2) {  // give a just-created segment a moment to be initialised
+      if (g_seg->magic.load(std::memory_order_acquire) == kMagic) { fresh = true; break; }
+      usleep(200);
+    }
+    if (fresh) {
+      const int pid = g_seg->creator_pid.load();
+      const bool alive = pid > 0 && (kill(pid, 0) == 0 || errno == EPERM);
+      if (alive && g_seg->attached.fetch_add(1) < g_size) break;  // ours
+    }
+    munmap(g_seg, sizeof(Segment));
+    g_seg = nullptr;
+    if (now_s() - t_begin > g_timeout_s) {
+      fprintf(stderr, "[liger mpi shim] rank %d: only stale segments named %s\n", g_rank, buf);
       return MPI_ERR_OTHER;
     }
-  } else {
-    const double t0 = now_s();
-    while ((fd = shm_open(g_name.c_str(), O_RDWR, 0600)) < 0) {
-      usleep(1000);
-      if (now_s() - t0 > g_timeout_s) { fprintf(stderr, "[liger mpi shim] rank %d: no segment %s\n", g_rank, buf); return MPI_ERR_OTHER; }
-    }
-    struct stat st;
-    while (fstat(fd, &st) == 0 && (size_t)st.st_size < sizeof(Segment)) {
-      usleep(1000);
-      if (now_s() - t0 > g_timeout_s) return MPI_ERR_OTHER;
-    }
+    usleep(2000);
   }
-  void* p = mmap(nullptr, sizeof(Segment), PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
-  close(fd);
-  if (p == MAP_FAILED) { perror("[liger mpi shim] mmap"); return MPI_ERR_OTHER; }
-  g_seg = (Segment*)p;
-  if (g_rank == 0) {
-    g_seg->attached.store(0);
-    g_seg->bar_count.store(0);
-    g_seg->bar_gen.store(0);
-    g_seg->bc_seq.store(0);
-    g_seg->bc_acks.store(g_size - 1);
-    g_seg->magic.store(kMagic, std::memory_order_release);
-  } else {
-    if (!wait_until([] { return g_seg->magic.load(std::memory_order_acquire) == kMagic; }, "MPI_Init (segment not initialised)"))
-      return MPI_ERR_OTHER;
-  }
-  g_seg->attached.fetch_add(1);
   if (!wait_until([] { return g_seg->attached.load() >= g_size; }, "MPI_Init (waiting for all ranks)")) return MPI_ERR_OTHER;
   return MPI_SUCCESS;
 }

@@ -128,22 +128,69 @@ def cpu_port_tokens_per_s():
                         f"tokens/s = {s} / (t * 4 layers), extrapolated to the 4-layer stack"))
 
 
-def run_reference_arm(args, rank):
-    """The reference has no CPU implementation of this path and its GPU build needs MPI, NCCL and cuBLAS;
-    this arm times the CPU port of its arithmetic (the oracle) on the host cores."""
+REF_HARNESS = os.path.join(ROOT, "oracle", "_ref", "liger_ref_harness")
+
+
+def run_reference_gpu_build(args, rank, world):
+    """The reference's own NCCL + cuBLAS build (unmodified sources + oracle/ref_harness/harness.cu, compiled
+    for sm_100a into oracle/_ref/), one process per GPU over the MPI stand-in.  The reference can only
+    express its own layer (post-LayerNorm, no residual, GELU with a 4H FFN, full attention through a mask
+    tensor); at hidden 12288 that layer has the same GEMM FLOPs as the GeGLU-32768 layer of this
+    benchmark, so tokens/s are comparable.  Returns the harness's JSON record (rank 0) or None."""
+    env = dict(os.environ)
+    env["LIGER_MPI_RANK"], env["LIGER_MPI_SIZE"] = str(rank), str(world)
+    env["LIGER_MPI_JOB"] = "bench_ref_%s" % os.environ.get("MASTER_PORT", "0")
+    env.setdefault("LIGER_MPI_TIMEOUT_S", "120")
+    W = WORKLOAD
+    cmd = [REF_HARNESS, str(W["batch"]), str(W["seq"]), str(W["heads"]), str(W["head_dim"]), str(args.layers),
+           str(args.steps), str(max(args.warmup, 3))]
+    try:
+        res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    except (OSError, subprocess.TimeoutExpired) as e:
+        return {"error": f"{type(e).__name__}: {e}"} if rank == 0 else None
+    if rank != 0:
+        return None
+    for ln in res.stdout.splitlines():
+        if ln.startswith("{\"ref_harness\""):
+            rec = json.loads(ln)
+            if res.returncode == 0 and rec.get("cuda_error") == "no error":
+                return rec
+            return {"error": f"exit {res.returncode}, cuda_error {rec.get('cuda_error')}"}
+    return {"error": f"exit {res.returncode}: {(res.stderr or res.stdout)[-300:]}"}
+
+
+def run_reference_arm(args, rank, world):
+    """Reference arm.  Preferred: the reference's own GPU build (see run_reference_gpu_build).  The
+    reference has no CPU implementation of this path; when its GPU build is not available (not built,
+    or it fails on this box) the arm times the CPU port of its arithmetic (the oracle) instead."""
+    tokens = WORKLOAD["batch"] * WORKLOAD["seq"]
+    H = WORKLOAD["heads"] * WORKLOAD["head_dim"]
+    rec = run_reference_gpu_build(args, rank, world) if os.path.exists(REF_HARNESS) else (
+        {"error": "oracle/_ref/liger_ref_harness has not been built"} if rank == 0 else None)
     if rank != 0:
         return
-    base = cpu_port_tokens_per_s()
-    tokens = WORKLOAD["batch"] * WORKLOAD["seq"]
-    line = {
-        "impl": "reference", "metric": "tokens/s", "value": base["value"], "unit": "tokens/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * tokens / base["value"],
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD["name"], "tokens_per_step": tokens},
-        "cpu_baseline": base,
-        "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
-    }
+    base = {"impl": "reference", "metric": "tokens/s", "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "data": "synthetic"}
+    if rec and "error" not in rec:
+        line = dict(base, value=rec["tokens_per_s"], ms_per_step=rec["ms_per_step"], dtype="fp16 (fp16 accumulate, CUBLAS_COMPUTE_16F)",
+                    config={"workload": WORKLOAD["name"], "tokens_per_step": tokens, "parallelism": f"tp{world}",
+                            "graph": "the reference's own layer: post-LayerNorm, no residual, GELU FFN 4H (same GEMM FLOPs as "
+                                     "the GeGLU-32768 layer), full attention with an all-ones mask",
+                            "build": "unmodified reference sources + oracle/ref_harness/harness.cu, nvcc sm_100a, cuBLAS + NCCL, "
+                                     "MPI stand-in; kernel vector replayed in order on one stream (Scheduler::run_sequential)"},
+                    cpu_baseline={"value": rec["tokens_per_s"], "unit": "tokens/s", "cores": 0, "kind": "reference",
+                                  "sample": "the reference's GPU build (it has no CPU path): full workload, all steps"},
+                    e2e={"value": rec["tokens_per_s_e2e"], "unit": "tokens/s", "ms_per_step": rec["ms_per_step_e2e"],
+                         "h2d_bytes_per_step": tokens * H * 2 * world, "d2h_bytes_per_step": tokens * H * 2 * world},
+                    gpu_launches=rec["kernels_per_step"] * args.steps)
+    else:
+        cpu = cpu_port_tokens_per_s()
+        line = dict(base, value=cpu["value"], ms_per_step=1000.0 * tokens / cpu["value"], dtype="f32",
+                    config={"workload": WORKLOAD["name"], "tokens_per_step": tokens,
+                            "note": "reference GPU build unavailable: " + (rec or {}).get("error", "unknown")},
+                    cpu_baseline=cpu,
+                    e2e={"value": cpu["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                    gpu_launches=0)
     print(json.dumps(line), flush=True)
 
 
@@ -160,7 +207,7 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", str(rank)))
     if args.impl == "reference":
-        run_reference_arm(args, rank)
+        run_reference_arm(args, rank, world)
         return
     if world != args.gpus:
         if args.gpus != 1 or world != 1:

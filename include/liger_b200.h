@@ -365,6 +365,14 @@ LIGER_API int liger_model_forward(liger_model* model, const void* input, void* o
  */
 LIGER_API int liger_model_set_micro_batches(liger_model* model, int micro_batches);
 
+/* Diagnostics for interleaved passes: with enable != 0 the next interleaved pass records an event
+ * before and after every kernel on its own stream; a later call returns, for the last such pass,
+ * kernel name, stream index and the enqueue-order event times in ms since the pass started (up to
+ * `capacity` entries; returns the count).  Event times bound a kernel's execution from above: a
+ * kernel may wait between its "before" event and its actual start. */
+LIGER_API int liger_model_timeline(liger_model* model, int enable, int capacity, int* names, int* streams,
+                                   double* start_ms, double* end_ms);
+
 /* Same with HOST buffers, all on `stream`; returns after enqueueing (synchronise the stream before
  * reading host_output).  world_size == 1: the whole input is copied to the device and the whole
  * result back.  world_size > 1: every rank passes the same full host input but uploads only its
