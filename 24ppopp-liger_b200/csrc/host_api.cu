@@ -274,6 +274,35 @@ extern "C" int liger_model_timeline(liger_model* m, int enable, int capacity, in
   return n;
 }
 
+extern "C" int liger_model_decode(liger_model* m, const void* input, void* output, int batch, int kv_len, int slot,
+                                  void* stream) {
+  if (!m || !input || !output) return liger::set_error(LIGER_ERR_INVALID, "model_decode: null argument");
+  try {
+    std::vector<FuncWrap> vec = m->model->forward_decode(input, output, batch, kv_len, slot);
+    DynamicNvInitParam dp;
+    dp.stream = stream;
+    int n = 0;
+    for (auto& f : vec) {
+      const int rc = f.callback(dp);
+      if (rc != LIGER_OK) return rc;
+      ++n;
+    }
+    return n;
+  } catch (const std::exception& e) {
+    return liger::set_error(LIGER_ERR_INVALID, "model_decode: %s", e.what());
+  }
+}
+
+extern "C" int liger_model_fill_kv_cache(liger_model* m) {
+  if (!m) return liger::set_error(LIGER_ERR_INVALID, "model_fill_kv_cache: null model");
+  try {
+    m->model->fill_kv_cache_seeded();
+    return LIGER_OK;
+  } catch (const std::exception& e) {
+    return liger::set_error(LIGER_ERR_INVALID, "model_fill_kv_cache: %s", e.what());
+  }
+}
+
 extern "C" int liger_model_set_micro_batches(liger_model* m, int micro_batches) {
   if (!m || micro_batches < 1 || micro_batches > 8) return liger::set_error(LIGER_ERR_INVALID, "model_set_micro_batches: 1..8");
   m->micro_batches = micro_batches;

@@ -232,6 +232,42 @@ class Bert_MHA {
     return vec;
   }
 
+  // One decode step (no counterpart in the reference, which has no KV cache): one new token per
+  // sequence.  Kernel 0 appends the token's K and V to the cache at position kv_len, kernel 1 is the
+  // split-KV decode attention over kv_len + 1 positions; kernels 2-3 are the prefill ones with M = batch.
+  std::vector<FuncWrap> forward_decode(const void* input, Workspace& w, const PostOp& post, const Shape& sh, half_t* k_cache,
+                                       half_t* v_cache, int kv_len, int kv_cap) const {
+    std::vector<FuncWrap> vec;
+    const int M = sh.batch, ws = SParam.world_size;
+    {
+      GEMM_ARGS a = linear_qkv_col->args(input, nullptr, M, 0);
+      a.epilogue = LIGER_EPI_QKV_SPLIT; a.bias = qkv_bias;
+      a.q_out = w.q; a.k_out = k_cache; a.v_out = v_cache;
+      a.seq_len = 1; a.heads = heads_local; a.head_dim = D; a.kv_stride = kv_cap; a.kv_pos = kv_len;
+      vec.push_back(make_gemm(0, 1.0f, a));
+    }
+    {
+      const half_t* q = w.q; half_t* o = w.attn; float* scratch = w.decode_scratch;
+      const int hl = heads_local, d = D, ldo = Hl, B = sh.batch, L = kv_len + 1;
+      const float sc = scalar;
+      vec.push_back(FuncWrap(1, 0.3f, COMPUTATION, [=](const DynamicNvInitParam& dp) {
+        return liger_attention_decode(q, k_cache, v_cache, o, scratch, B, hl, L, kv_cap, d, ldo, sc, dp.stream);
+      }));
+    }
+    {
+      GEMM_ARGS a = linear_w_row->args(w.attn, w.partial, M);
+      if (ws == 1 && post.residual_in) {
+        a.epilogue = LIGER_EPI_RESIDUAL; a.bias = post.bias; a.residual = post.residual_in; a.ldr = n; a.c = w.hidden;
+      } else if (ws > 1 && !is_one_shot(M, n)) {
+        a.epilogue = LIGER_EPI_SCATTER; a.scatter_comm = SParam.comm; a.scatter_off = w.partial_off;
+      }
+      vec.push_back(make_gemm(2, 2.0f, a));
+    }
+    Shape flat{sh.batch, 1, sh.slot};
+    vec.push_back(post_kernel(3, w, post, flat, SParam, n));
+    return vec;
+  }
+
   // kernel 3 / 6: fused all-reduce (+ residual) + LayerNorm, or a plain LayerNorm when world_size == 1
   static FuncWrap post_kernel(int name, Workspace& w, const PostOp& post, const Shape& sh, const StaticNvInitParam& sp,
                               int n) {
@@ -420,6 +456,71 @@ class Bert_Model {
     return vec;
   }
 
+  // One decode step for `batch` sequences whose caches hold kv_len positions: input / output are
+  // [batch, H]; pre-LayerNorm graph only.  The caches must have been created (kv_capacity > 0).
+  std::vector<FuncWrap> forward_decode(const void* input, void* output, int batch_size, int kv_len, int slot = -1) {
+    if (BertParams.graph != GRAPH_PRELN) throw std::runtime_error("Bert_Model::forward_decode: pre-LayerNorm graph only");
+    if (BertParams.kv_capacity <= 0 || kv_len < 0 || kv_len + 1 > BertParams.kv_capacity)
+      throw std::runtime_error("Bert_Model::forward_decode: kv_len + 1 exceeds the KV-cache capacity");
+    if (batch_size < 1 || batch_size > BertParams.max_batch_size)
+      throw std::runtime_error("Bert_Model::forward_decode: batch outside the configured maximum");
+    if (slot < 0) { slot = next_slot; next_slot = (next_slot + 1) % (int)slots.size(); }
+    Workspace& w = slots.at(slot);
+    const Shape sh{batch_size, 1, slot};
+    const int ws = SParam.world_size, L = BertParams.layer_num, M = batch_size;
+    std::vector<FuncWrap> vec;
+    vec.push_back(encoders[0]->ln_mha->forward(kPrologueName, input, w.normed, M));
+    const void* resid = input;
+    for (int l = 0; l < L; ++l) {
+      const Bert_Encoder* e = encoders[l];
+      const bool last = (l == L - 1);
+      PostOp mha_post, mlp_post;
+      mha_post.residual_in = resid; mha_post.bias = e->MHA->w_bias;
+      mha_post.gamma = e->ln_mlp->gamma; mha_post.beta = e->ln_mlp->beta;
+      mha_post.out = w.normed; mha_post.out_off = w.normed_off;
+      mlp_post.residual_in = w.hidden; mlp_post.bias = e->MLP->down_bias;
+      if (!last) {
+        mlp_post.gamma = encoders[l + 1]->ln_mha->gamma; mlp_post.beta = encoders[l + 1]->ln_mha->beta;
+        mlp_post.out = w.normed; mlp_post.out_off = w.normed_off;
+      } else {
+        mlp_post.out = w.xbuf; mlp_post.out_off = w.xbuf_off;
+        if (ws == 1) mlp_post.direct_out = output;
+      }
+      std::vector<FuncWrap> t = e->MHA->forward_decode(w.normed, w, mha_post, sh, e->k_cache, e->v_cache, kv_len,
+                                                       BertParams.kv_capacity);
+      vec.insert(vec.end(), t.begin(), t.end());
+      t = e->MLP->forward(w.normed, w, mlp_post, sh);
+      vec.insert(vec.end(), t.begin(), t.end());
+      resid = w.hidden;
+    }
+    if (ws > 1) {
+      const void* src = w.xbuf; const size_t bytes = (size_t)M * H * 2;
+      vec.push_back(FuncWrap(kEpilogueName, 0.05f, COMPUTATION, [=](const DynamicNvInitParam& dp) {
+        cudaError_t err = cudaMemcpyAsync(output, src, bytes, cudaMemcpyDeviceToDevice, (cudaStream_t)dp.stream);
+        return err == cudaSuccess ? LIGER_OK : LIGER_ERR_CUDA;
+      }));
+    }
+    return vec;
+  }
+
+  // Fills every layer's KV cache with the seeded N(0,1) tensors (ids 0x10001 + 2*layer for keys,
+  // 0x10002 + 2*layer for values; logical layout [batch][heads][kv_capacity][head_dim], this rank
+  // keeping its own heads).
+  void fill_kv_cache_seeded() {
+    const int cap = BertParams.kv_capacity, hl = heads_local, heads = BertParams.head_num, r = SParam.world_rank;
+    if (cap <= 0) throw std::runtime_error("Bert_Model::fill_kv_cache_seeded: no KV cache configured");
+    for (int l = 0; l < BertParams.layer_num; ++l)
+      for (int b = 0; b < BertParams.max_batch_size; ++b) {
+        // rows = this rank's heads x cap positions, D columns; logical row index = (b*heads + head)*cap + pos
+        half_t* kd = encoders[l]->k_cache + (size_t)b * hl * cap * D;
+        half_t* vd = encoders[l]->v_cache + (size_t)b * hl * cap * D;
+        const int row0 = (b * heads + r * hl) * cap;
+        fill(kd, hl * cap, D, D, row0, 0, D, 0x10001u + 2u * (uint32_t)l, 0.0f, 1.0f, 0);
+        fill(vd, hl * cap, D, D, row0, 0, D, 0x10002u + 2u * (uint32_t)l, 0.0f, 1.0f, 0);
+      }
+    cuda_check(cudaDeviceSynchronize(), "fill_kv_cache_seeded");
+  }
+
   // number of distinct kernel names a request can contain (profile dictionary keys 0 .. n-1)
   int kernel_names() const { return kEpilogueName + 1; }
 
@@ -507,6 +608,11 @@ class Bert_Model {
       w.v = device_alloc<half_t>(M * Hl, "ws.v");
       w.attn = device_alloc<half_t>(M * Hl, "ws.attn");
       w.act = device_alloc<half_t>(M * Fl, "ws.act");
+      if (BertParams.kv_capacity > 0) {
+        const size_t bytes = liger_attention_decode_scratch_bytes(BertParams.max_batch_size, heads_local, D,
+                                                                  BertParams.kv_capacity);
+        w.decode_scratch = (float*)device_alloc<uint8_t>(bytes, "ws.decode_scratch");
+      }
       slots.push_back(w);
     }
   }

@@ -354,6 +354,20 @@ LIGER_API int liger_model_destroy(liger_model* model);
 LIGER_API int liger_model_forward(liger_model* model, const void* input, void* output, int batch, int seq_len, int slot,
                                   void* stream);
 /*
+ * One decode step: `batch` sequences, one new token each (input / output [batch, hidden]), against
+ * the model's KV caches holding kv_len positions (cfg.kv_capacity > kv_len; pre-LayerNorm graph).
+ * Per layer the token's K and V are appended at position kv_len by the QKV GEMM's epilogue and a
+ * split-KV attention kernel streams the cache once.  liger_model_fill_kv_cache() loads the caches
+ * with seeded N(0,1) values (tensor ids 0x10001 + 2*layer / 0x10002 + 2*layer, logical layout
+ * [batch][heads][kv_capacity][head_dim]).  The reference has no decode path or KV cache; these two
+ * entry points exist for the decode configuration of the benchmark suite.  Returns the number of
+ * kernels launched.
+ */
+LIGER_API int liger_model_decode(liger_model* model, const void* input, void* output, int batch, int kv_len, int slot,
+                                 void* stream);
+LIGER_API int liger_model_fill_kv_cache(liger_model* model);
+
+/*
  * Interleaving inside one request.  With micro_batches = n > 1 and world_size > 1, a forward pass
  * whose batch divides by n is split into n micro-requests (consecutive groups of sequences) that
  * run on n internal streams and n consecutive workspace slots starting at `slot`, launched

@@ -175,3 +175,11 @@ def stack_forward(cfg: Config, x, B, S, mask=None):
     m = _f32(mask) if mask is not None else None
     lib().lo_stack_forward(C.byref(cfg), _p(x), _p(m), _p(out), B, S)
     return out
+
+
+def stack_decode(cfg: Config, x, B, kv_len, kv_cap):
+    """One decode step of the pre-LN stack against the seeded KV cache (see lo_stack_decode)."""
+    x = _f32(x)
+    out = np.empty_like(x)
+    lib().lo_stack_decode(C.byref(cfg), _p(x), _p(out), B, kv_len, kv_cap)
+    return out

@@ -460,3 +460,97 @@ LO_API void lo_stack_forward(const lo_config* cfg, const float* x, const float* 
   free(hbuf); free(nbuf); free(part); free(red); free(W); free(W2); free(lin); free(qb); free(kb); free(vb);
   free(ab); free(am); free(act); free(bias); free(g); free(be);
 }
+
+
+/*
+ * One decode step: a single new token per sequence (x is [B, H]) against a seeded KV cache holding
+ * kv_len positions per sequence, on the pre-LayerNorm graph (cfg->graph must be 1).  The reference
+ * has no KV cache or decode path; the step is defined by the benchmark configuration: per layer the
+ * new token's K and V are appended at position kv_len and the query attends to positions 0..kv_len.
+ * The cache of layer l is the seeded tensor LO_KCACHE + 2*l (keys) / LO_VCACHE + 2*l (values) with
+ * logical layout [B][heads][kv_cap][head_dim], N(0,1); rank r owns heads [r*h/ws, (r+1)*h/ws).
+ */
+LO_API void lo_stack_decode(const lo_config* cfg, const float* x, float* out, int B, int kv_len, int kv_cap) {
+  const int H = cfg->hidden, D = cfg->head_dim, ws = cfg->tp, F = cfg->ffn_inner, heads = cfg->heads;
+  const int hl = heads / ws, Hl = H / ws, Fl = F / ws;
+  const int M = B, L = kv_len + 1;
+  const int upw = cfg->act ? 2 * F : F;
+  const float scale = 1.0f / sqrtf((float)D);
+  const int r16 = cfg->round16;
+  float* hbuf = falloc((size_t)M * H); float* nbuf = falloc((size_t)M * H);
+  float* part = falloc((size_t)ws * M * H); float* red = falloc((size_t)M * H);
+  const int wmax = Fl > Hl ? Fl : Hl, linmax = 2 * Fl > Hl ? 2 * Fl : Hl;
+  float* W = falloc((size_t)H * wmax); float* W2 = falloc((size_t)wmax * H); float* lin = falloc((size_t)M * linmax);
+  float* qb = falloc((size_t)M * Hl); float* kn = falloc((size_t)M * Hl); float* vn = falloc((size_t)M * Hl);
+  float* kc = falloc((size_t)B * hl * L * D); float* vc = falloc((size_t)B * hl * L * D);
+  float* ab = falloc((size_t)M * Hl); float* act = falloc((size_t)M * Fl);
+  float* bias = falloc((size_t)(2 * F > H ? 2 * F : H)); float* g = falloc(H); float* be = falloc(H);
+  memcpy(hbuf, x, sizeof(float) * (size_t)M * H);
+  for (int l = 0; l < cfg->layers; ++l) {
+    const uint32_t id0 = (uint32_t)l * 32u;
+    lo_fill_normal_f32(g, H, cfg->seed, id0 + LO_LN1_G, 0, 1.0f, LO_W_STD);
+    lo_fill_normal_f32(be, H, cfg->seed, id0 + LO_LN1_B, 0, 0.0f, LO_W_STD);
+    lo_layernorm(hbuf, g, be, nbuf, M, H);
+    maybe_round(nbuf, (size_t)M * H, r16);
+    for (int r = 0; r < ws; ++r) {
+      const uint32_t wid[3] = {LO_WQ, LO_WK, LO_WV}, bid[3] = {LO_BQ, LO_BK, LO_BV};
+      float* dst[3] = {qb, kn, vn};
+      for (int t = 0; t < 3; ++t) {
+        lo_fill_normal_window_f32(W, H, Hl, 0, r * Hl, H, cfg->seed, id0 + wid[t], 0.0f, LO_W_STD);
+        lo_linear(nbuf, H, W, Hl, lin, Hl, M, Hl, H);
+        lo_fill_normal_f32(bias, Hl, cfg->seed, id0 + bid[t], (uint64_t)r * Hl, 0.0f, LO_W_STD);
+        lo_add_bias_split_heads(lin, Hl, bias, dst[t], B, 1, hl, D);   /* [B, hl, 1, D] */
+        maybe_round(dst[t], (size_t)M * Hl, r16);
+      }
+      /* this rank's heads of the cache, positions 0..kv_len-1, then the new token's K / V */
+      for (int b = 0; b < B; ++b)
+        for (int hh = 0; hh < hl; ++hh) {
+          const uint64_t base = (((uint64_t)b * heads + (uint64_t)(r * hl + hh)) * kv_cap) * D;
+          float* kd = kc + ((size_t)b * hl + hh) * L * D;
+          float* vd = vc + ((size_t)b * hl + hh) * L * D;
+          lo_fill_normal_f32(kd, (uint64_t)kv_len * D, cfg->seed, LO_KCACHE + 2u * (uint32_t)l, base, 0.0f, 1.0f);
+          lo_fill_normal_f32(vd, (uint64_t)kv_len * D, cfg->seed, LO_VCACHE + 2u * (uint32_t)l, base, 0.0f, 1.0f);
+          memcpy(kd + (size_t)kv_len * D, kn + ((size_t)b * hl + hh) * D, sizeof(float) * D);
+          memcpy(vd + (size_t)kv_len * D, vn + ((size_t)b * hl + hh) * D, sizeof(float) * D);
+        }
+      lo_attention(qb, kc, vc, NULL, 1, ab, B, hl, 1, L, D, scale);   /* [B, hl, 1, D] == [B, hl*D] */
+      maybe_round(ab, (size_t)M * Hl, r16);
+      lo_fill_normal_window_f32(W2, Hl, H, r * Hl, 0, H, cfg->seed, id0 + LO_WO, 0.0f, LO_W_STD);
+      lo_linear(ab, Hl, W2, H, part + (size_t)r * M * H, H, M, H, Hl);
+      maybe_round(part + (size_t)r * M * H, (size_t)M * H, r16);
+    }
+    lo_allreduce_sum(part, red, ws, (uint64_t)M * H);
+    lo_fill_normal_f32(bias, H, cfg->seed, id0 + LO_BO, 0, 0.0f, LO_W_STD);
+    lo_fill_normal_f32(g, H, cfg->seed, id0 + LO_LN2_G, 0, 1.0f, LO_W_STD);
+    lo_fill_normal_f32(be, H, cfg->seed, id0 + LO_LN2_B, 0, 0.0f, LO_W_STD);
+    lo_add_bias_input_layernorm_2(red, g, be, bias, hbuf, nbuf, M, H, r16);
+    maybe_round(nbuf, (size_t)M * H, r16);
+    for (int r = 0; r < ws; ++r) {
+      if (cfg->act == 0) {
+        lo_fill_normal_window_f32(W, H, Fl, 0, r * Fl, upw, cfg->seed, id0 + LO_WUP, 0.0f, LO_W_STD);
+        lo_linear(nbuf, H, W, Fl, lin, Fl, M, Fl, H);
+        lo_fill_normal_f32(bias, Fl, cfg->seed, id0 + LO_BUP, (uint64_t)r * Fl, 0.0f, LO_W_STD);
+        lo_add_bias_gelu(lin, bias, M, Fl);
+        memcpy(act, lin, sizeof(float) * (size_t)M * Fl);
+      } else {
+        lo_fill_normal_window_f32(W, H, Fl, 0, r * Fl, upw, cfg->seed, id0 + LO_WUP, 0.0f, LO_W_STD);
+        lo_linear(nbuf, H, W, Fl, lin, 2 * Fl, M, Fl, H);
+        lo_fill_normal_window_f32(W, H, Fl, 0, F + r * Fl, upw, cfg->seed, id0 + LO_WUP, 0.0f, LO_W_STD);
+        lo_linear(nbuf, H, W, Fl, lin + Fl, 2 * Fl, M, Fl, H);
+        lo_fill_normal_f32(bias, Fl, cfg->seed, id0 + LO_BUP, (uint64_t)r * Fl, 0.0f, LO_W_STD);
+        lo_fill_normal_f32(bias + Fl, Fl, cfg->seed, id0 + LO_BUP, (uint64_t)F + (uint64_t)r * Fl, 0.0f, LO_W_STD);
+        lo_add_bias_geglu(lin, bias, act, M, Fl);
+      }
+      maybe_round(act, (size_t)M * Fl, r16);
+      lo_fill_normal_window_f32(W2, Fl, H, r * Fl, 0, H, cfg->seed, id0 + LO_WDOWN, 0.0f, LO_W_STD);
+      lo_linear(act, Fl, W2, H, part + (size_t)r * M * H, H, M, H, Fl);
+      maybe_round(part + (size_t)r * M * H, (size_t)M * H, r16);
+    }
+    lo_allreduce_sum(part, red, ws, (uint64_t)M * H);
+    lo_fill_normal_f32(bias, H, cfg->seed, id0 + LO_BDOWN, 0, 0.0f, LO_W_STD);
+    lo_add_bias_input_layernorm_2(red, NULL, NULL, bias, hbuf, NULL, M, H, r16);
+  }
+  memcpy(out, hbuf, sizeof(float) * (size_t)M * H);
+  free(hbuf); free(nbuf); free(part); free(red); free(W); free(W2); free(lin); free(qb); free(kn); free(vn);
+  free(kc); free(vc); free(ab); free(act); free(bias); free(g); free(be);
+}

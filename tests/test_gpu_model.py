@@ -166,3 +166,30 @@ def test_stack_forward_tensor_parallel_2(oracle, case):
     assert np.array_equal(results[0], results[1])
     # tensor parallelism does not change the result beyond rounding: TP=2 vs the TP=1 oracle
     assert max_rel_err(results[0], oracle_out(oracle, case, 1, 0)) < 1e-2
+
+
+@pytest.mark.parametrize("B,kv_len,cap,heads,D,F,act", [(4, 300, 512, 8, 128, 2048, 1), (3, 17, 64, 4, 64, 1024, 0)])
+def test_decode_step_single_gpu(gpu, liger, oracle, B, kv_len, cap, heads, D, F, act):
+    """BASELINE config 3 in miniature: one new token per sequence against a seeded N(0,1) KV cache."""
+    import torch
+    H = heads * D
+    cfg = liger.default_config(max_batch_size=B, max_seq_len=8, head_num=heads, size_per_head=D, layer_num=2, graph=1,
+                               act=act, ffn_inner=F, causal=1, seed=0, workspace_slots=2, schedule_deep=1, kv_capacity=cap)
+    model = C.c_void_p()
+    liger.check(gpu.liger_model_create(C.byref(model), C.byref(cfg), 0, 1, None))
+    liger.check(gpu.liger_model_fill_kv_cache(model))
+    x = dev_fill(liger, B, H, 0, oracle.INPUT)
+    out = torch.zeros((B, H), dtype=torch.float16, device="cuda")
+    n = liger.check(gpu.liger_model_decode(model, ptr(x), ptr(out), B, kv_len, 0, stream_ptr()))
+    torch.cuda.synchronize()
+    assert n == 7 * 2
+    ocfg = oracle.Config(hidden=H, heads=heads, head_dim=D, ffn_inner=F, layers=2, tp=1, graph=1, act=act, causal=1,
+                         round16=0, seed=0)
+    want = oracle.stack_decode(ocfg, to_np(x), B, kv_len, cap)
+    assert_close(to_np(out), want, rel=1e-2, what="decode step")
+    # the step appended the token's K/V: a second step at kv_len + 1 must see them (result changes, stays finite)
+    out2 = torch.zeros_like(out)
+    liger.check(gpu.liger_model_decode(model, ptr(x), ptr(out2), B, kv_len + 1, 0, stream_ptr()))
+    assert torch.isfinite(out2.float()).all() and not torch.equal(out2, out)
+    assert gpu.liger_model_decode(model, ptr(x), ptr(out), B, cap, 0, stream_ptr()) == -1   # cache full
+    gpu.liger_model_destroy(model)
