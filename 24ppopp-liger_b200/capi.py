@@ -92,6 +92,7 @@ SIGNATURES = {
     "liger_comm_timing": (_I, [_P, _I, _I, C.POINTER(C.c_double * 4)]),
     "liger_comm_rank": (_I, [_P]),
     "liger_comm_world_size": (_I, [_P]),
+    "liger_allreduce_ce": (_I, [_P, _I, _SZ, _SZ, _SZ, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "liger_allreduce_fused": (_I, [_P, _I, _SZ, _SZ, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "liger_model_config_init": (None, [C.POINTER(ModelConfig)]),
     "liger_model_comm_bytes": (_SZ, [C.POINTER(ModelConfig), _I]),

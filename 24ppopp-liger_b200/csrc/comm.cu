@@ -99,12 +99,13 @@ __global__ void allreduce_entry_barrier_kernel(CommDev c, int channel, uint32_t 
 }
 
 __global__ void __launch_bounds__(kArThreads, 2)
-allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t out_off,
+allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t recv_off, size_t out_off,
                        const __half* residual_in, __half* hidden,
                        const __half* __restrict__ bias, const __half* __restrict__ gamma,
                        const __half* __restrict__ beta, int n, int row_lo, int row_hi, int one_shot, int rows_per_rank,
                        uint32_t epoch_in,
-                       uint32_t epoch_out, unsigned int* done_counter, unsigned long long* stamps, DeviceStatus* st) {
+                       uint32_t epoch_out, unsigned int* done_counter, unsigned long long* stamps, DeviceStatus* st,
+                       int skip_exit_barrier) {
   __shared__ float red[32];
   __shared__ int s_fail;
   __shared__ int s_last;
@@ -132,10 +133,16 @@ allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t out_of
       int p = first + kx;
       if (p >= c.ws) p -= c.ws;
       // mode 3: the producing GEMMs already stored every rank's rows for this owner into local slots
-      const __half* src = one_shot == 3
-                              ? reinterpret_cast<const __half*>(c.base[c.rank] + partial_off) +
-                                    ((size_t)p * rows_per_rank + (row - c.rank * rows_per_rank)) * n
-                              : reinterpret_cast<const __half*>(c.base[p] + partial_off) + roff;
+      // mode 4: peers' rows were copied into local receive slots by the copy engines; own rows are
+      // read from the own partial in place
+      const __half* src =
+          one_shot == 3 ? reinterpret_cast<const __half*>(c.base[c.rank] + partial_off) +
+                              ((size_t)p * rows_per_rank + (row - c.rank * rows_per_rank)) * n
+          : one_shot == 4
+              ? (p == c.rank ? reinterpret_cast<const __half*>(c.base[c.rank] + partial_off) + roff
+                             : reinterpret_cast<const __half*>(c.base[c.rank] + recv_off) +
+                                   ((size_t)p * rows_per_rank + (row - c.rank * rows_per_rank)) * n)
+              : reinterpret_cast<const __half*>(c.base[p] + partial_off) + roff;
 #pragma unroll
       for (int i = 0; i < kArMaxVec; ++i) {
         const int idx = threadIdx.x + i * kArThreads;
@@ -230,7 +237,7 @@ allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t out_of
 #pragma unroll
           for (int j = 0; j < 4; ++j) ow[j] = pack_half2(v[i][2 * j], v[i][2 * j + 1]);
         }
-        if (one_shot == 1) {
+        if (one_shot == 1 || one_shot == 4) {
           *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(c.base[c.rank] + out_off) + roff + (size_t)idx * 8) = o;
         } else {
           for (int kx = 0; kx < c.ws; ++kx) {
@@ -251,7 +258,9 @@ allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t out_of
     if (ticket == gridDim.x - 1) { *done_counter = 0u; s_last = 1; }
   }
   __syncthreads();
-  if (s_last) {
+  if (s_last && skip_exit_barrier) {
+    if (threadIdx.x == 0) { stamps[2] = globaltimer_ns(); stamps[5] += stamps[2] - stamps[1]; stamps[7] += 1ull; }
+  } else if (s_last) {
     const unsigned long long t_work = globaltimer_ns();
     __threadfence_system();
     barrier_signal(c, channel, epoch_out);
@@ -438,8 +447,100 @@ extern "C" int liger_allreduce_fused(liger_comm* c, int channel, size_t partial_
   int rc = check_launch("allreduce_entry_barrier_kernel");
   if (rc != LIGER_OK) return rc;
   allreduce_fused_kernel<<<grid, kArThreads, 0, (cudaStream_t)stream>>>(
-      cd, channel, kFlagRegionBytes + partial_off, kFlagRegionBytes + out_off, (const __half*)residual_in, (__half*)hidden, (const __half*)bias,
+      cd, channel, kFlagRegionBytes + partial_off, 0, kFlagRegionBytes + out_off, (const __half*)residual_in, (__half*)hidden, (const __half*)bias,
       (const __half*)gamma, (const __half*)beta, n, lo, hi, one_shot, rpr_all, e_in, e_out, c->done + channel,
-      c->stamps + 8 * channel, dev->status_dev);
+      c->stamps + 8 * channel, dev->status_dev, 0);
   return check_launch("allreduce_fused_kernel");
+}
+
+// ---- the same collective with the data movement on the copy engines ------------------------------------
+// A stand-alone barrier (one warp): used after copy-engine transfers, which cannot signal by themselves.
+namespace liger {
+__global__ void comm_barrier_kernel(CommDev c, int channel, uint32_t epoch, unsigned long long* stamps, int stamp_slot,
+                                    DeviceStatus* st, unsigned int where) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  const unsigned long long t0 = globaltimer_ns();
+  __threadfence_system();
+  barrier_signal(c, channel, epoch);
+  barrier_wait(c, channel, epoch, &s_fail, st, where);
+  if (threadIdx.x == 0) {
+    const unsigned long long t1 = globaltimer_ns();
+    if (stamp_slot == 4) { stamps[0] = t0; stamps[1] = t1; }
+    stamps[stamp_slot] += t1 - t0;
+  }
+}
+}  // namespace liger
+
+extern "C" int liger_allreduce_ce(liger_comm* c, int channel, size_t partial_off, size_t recv_off, size_t out_off,
+                                  const void* residual_in, void* hidden, const void* bias, const void* gamma,
+                                  const void* beta, int m, int n, int row_begin, int row_end, void* stream) {
+  if (!c) return set_error(LIGER_ERR_INVALID, "allreduce_ce: null communicator");
+  if (!c->connected) return set_error(LIGER_ERR_COMM, "allreduce_ce: communicator is not connected");
+  if (channel < 0 || channel >= c->channels) return set_error(LIGER_ERR_INVALID, "allreduce_ce: channel %d of %d", channel, c->channels);
+  if (m <= 0 || n <= 0 || n % 8 || n > kArThreads * kArMaxVec * 8)
+    return set_error(LIGER_ERR_UNSUPPORTED, "allreduce_ce: n = %d must be a multiple of 8 and <= %d", n, kArThreads * kArMaxVec * 8);
+  if (row_begin < 0 || row_end > m || row_begin > row_end) return set_error(LIGER_ERR_INVALID, "allreduce_ce: bad row range");
+  const int ws = c->ws, rank = c->rank;
+  const int rpr = (m + ws - 1) / ws;
+  const size_t bytes = (size_t)m * n * 2, recv_bytes = (size_t)ws * rpr * n * 2;
+  if (partial_off % 16 || out_off % 16 || recv_off % 16 || partial_off + bytes > c->data_bytes ||
+      out_off + bytes > c->data_bytes || recv_off + recv_bytes > c->data_bytes)
+    return set_error(LIGER_ERR_INVALID, "allreduce_ce: regions must be 16-byte aligned and inside the %zu-byte data region", c->data_bytes);
+  if ((gamma == nullptr) != (beta == nullptr)) return set_error(LIGER_ERR_INVALID, "allreduce_ce: gamma and beta go together");
+  if (hidden && !residual_in) residual_in = hidden;
+  const DeviceInfo* dev = current_device();
+  if (!dev) return LIGER_ERR_CUDA;
+  cudaStream_t s = (cudaStream_t)stream;
+  CommDev cd;
+  for (int p = 0; p < kMaxRanks; ++p) cd.base[p] = p < ws ? c->peer[p] : nullptr;
+  cd.rank = rank; cd.ws = ws;
+  auto clip = [&](int owner, int& lo, int& hi) {
+    lo = owner * rpr > row_begin ? owner * rpr : row_begin;
+    const int oh = (owner + 1) * rpr < m ? (owner + 1) * rpr : m;
+    hi = oh < row_end ? oh : row_end;
+    if (hi < lo) hi = lo;
+  };
+  // 1. reduce-scatter: my rows of every peer's slice go to that peer's receive slot for me
+  for (int k = 1; k < ws; ++k) {
+    const int p = (rank + k) % ws;
+    int lo, hi;
+    clip(p, lo, hi);
+    if (hi > lo)
+      LIGER_CUDA_TRY(cudaMemcpyAsync(c->peer[p] + kFlagRegionBytes + recv_off + ((size_t)rank * rpr + (lo - p * rpr)) * n * 2,
+                                     c->local + kFlagRegionBytes + partial_off + (size_t)lo * n * 2, (size_t)(hi - lo) * n * 2,
+                                     cudaMemcpyDefault, s));
+  }
+  const uint32_t e_in = ++c->epoch[channel];
+  const uint32_t e_out = ++c->epoch[channel];
+  comm_barrier_kernel<<<1, 32, 0, s>>>(cd, channel, e_in, c->stamps + 8 * channel, 4, dev->status_dev, 0x210u);
+  int rc = check_launch("comm_barrier_kernel");
+  if (rc != LIGER_OK) return rc;
+  // 2. local reduction (+ residual + LayerNorm) of the rows this rank owns, result stored locally
+  int lo, hi;
+  clip(rank, lo, hi);
+  int grid = hi - lo;
+  static int max_ctas = -1;
+  if (max_ctas < 0) {
+    const char* e = getenv("LIGER_AR_MAX_CTAS");
+    max_ctas = (e && atoi(e) > 0) ? atoi(e) : dev->sm_count * 4;
+  }
+  if (grid > max_ctas) grid = max_ctas;
+  if (grid < 1) grid = 1;
+  allreduce_fused_kernel<<<grid, kArThreads, 0, s>>>(
+      cd, channel, kFlagRegionBytes + partial_off, kFlagRegionBytes + recv_off, kFlagRegionBytes + out_off,
+      (const __half*)residual_in, (__half*)hidden, (const __half*)bias, (const __half*)gamma, (const __half*)beta, n, lo, hi, 4,
+      rpr, e_in, e_out, c->done + channel, c->stamps + 8 * channel, dev->status_dev, 1);
+  if ((rc = check_launch("allreduce_fused_kernel")) != LIGER_OK) return rc;
+  // 3. all-gather of the finished rows
+  for (int k = 1; k < ws; ++k) {
+    const int p = (rank + k) % ws;
+    if (hi > lo)
+      LIGER_CUDA_TRY(cudaMemcpyAsync(c->peer[p] + kFlagRegionBytes + out_off + (size_t)lo * n * 2,
+                                     c->local + kFlagRegionBytes + out_off + (size_t)lo * n * 2, (size_t)(hi - lo) * n * 2,
+                                     cudaMemcpyDefault, s));
+  }
+  comm_barrier_kernel<<<1, 32, 0, s>>>(cd, channel, e_out, c->stamps + 8 * channel, 6, dev->status_dev, 0x211u);
+  return check_launch("comm_barrier_kernel");
 }

@@ -21,12 +21,49 @@ struct GemmParams {
   int seq_len, heads, head_dim;
   int kv_stride, kv_pos;
   int tiles_m, tiles_n, kblocks;
+  // Tile order (see tile_coords): the smaller-footprint operand is kept L2-resident in panels
+  int panel_tiles;   // tiles of the stationary operand per panel
+  int stationary;    // 0: panels over M (A rows stay in L2, W^T streams), 1: panels over N
+  int use_hints;     // 1: L2 eviction-priority hints on the TMA loads
   // LIGER_EPI_SCATTER: row r goes to rank r / rows_per_rank, into that rank's receive slot for this rank
   uint8_t* peer[kMaxRanks];
   size_t scatter_off;
   int rank, rows_per_rank;
   DeviceStatus* status;
 };
+
+// host side (gemm_sm100.cu): fills p.stationary / p.panel_tiles
+void choose_tile_order(GemmParams& p, const liger_gemm_args& a, int tile_m, int tile_n);
+
+// Tile t of the launch -> (m tile, n tile).  All CTAs walk K in step, so the DRAM traffic of a GEMM
+// is decided by which operand rows the concurrently running tiles share and by what survives in L2
+// from one wave to the next.  Tiles are ordered in panels of `panel_tiles` tiles of the stationary
+// operand (sized on the host to about half of L2); inside a panel the stationary index runs
+// fastest, so every wave re-uses the same resident panel while the other operand streams through
+// once per panel.
+__device__ __forceinline__ void tile_coords(const GemmParams& p, int t, int& tm, int& tn) {
+  if (p.stationary == 0) {
+    const int per_panel = p.panel_tiles * p.tiles_n;
+    const int panel = t / per_panel;
+    const int within = t - panel * per_panel;
+    const int rows = min(p.panel_tiles, p.tiles_m - panel * p.panel_tiles);  // last panel may be short
+    tn = within / rows;
+    tm = panel * p.panel_tiles + (within - tn * rows);
+  } else {
+    const int per_panel = p.panel_tiles * p.tiles_m;
+    const int panel = t / per_panel;
+    const int within = t - panel * per_panel;
+    const int cols = min(p.panel_tiles, p.tiles_n - panel * p.panel_tiles);
+    tm = within / cols;
+    tn = panel * p.panel_tiles + (within - tm * cols);
+  }
+}
+
+// L2 eviction-priority descriptors for TMA loads (the fixed encodings CUDA's createpolicy produces
+// for fraction 1.0): the stationary operand is loaded evict_last, the streaming one evict_first.
+constexpr uint64_t kL2EvictFirst = 0x12F0000000000000ull;
+constexpr uint64_t kL2EvictLast = 0x14F0000000000000ull;
+constexpr uint64_t kL2EvictNormal = 0x1000000000000000ull;
 
 // ---- epilogue helpers -------------------------------------------------------------------------
 __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {

@@ -58,11 +58,12 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
 
 // per-CTA load of a 2-CTA MMA operand: the data goes to this CTA's shared memory, the completion
 // (transaction bytes) to the leader CTA's barrier
-__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* tmap, uint32_t leader_bar, int x, int y) {
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* tmap, uint32_t leader_bar, int x, int y,
+                                                 uint64_t hint) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
       :
-      : "r"(smem_u32(smem_dst)), "l"(tmap), "r"(leader_bar), "r"(x), "r"(y)
+      : "r"(smem_u32(smem_dst)), "l"(tmap), "r"(leader_bar), "r"(x), "r"(y), "l"(hint)
       : "memory");
 }
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_slot, uint32_t ncols) {
@@ -148,16 +149,20 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
+      const uint64_t hint_a = !p.use_hints ? kL2EvictNormal : p.stationary == 0 ? kL2EvictLast : kL2EvictFirst;
+      const uint64_t hint_b = !p.use_hints ? kL2EvictNormal : p.stationary == 0 ? kL2EvictFirst : kL2EvictLast;
       for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
-        const int m0 = (t % p.tiles_m) * kBM2 + (int)cta_rank * 128;
-        const int n0 = p.n_begin + (t / p.tiles_m) * kBN2 + (int)cta_rank * 128;
+        int tm, tn;
+        tile_coords(p, t, tm, tn);
+        const int m0 = tm * kBM2 + (int)cta_rank * 128;
+        const int n0 = p.n_begin + tn * kBN2 + (int)cta_rank * 128;
         for (int kb = 0; kb < p.kblocks; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
           const uint32_t leader_full = smem_u32(&full_bar[stage]) & 0xFEFFFFFFu;  // same offset in cluster rank 0
           if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);
-          tma_load_2d_pair(sa, &tmap_a, leader_full, kb * BK, m0);
-          tma_load_2d_pair(sa + Cfg::kABytes, &tmap_b, leader_full, kb * BK, n0);
+          tma_load_2d_pair(sa, &tmap_a, leader_full, kb * BK, m0, hint_a);
+          tma_load_2d_pair(sa + Cfg::kABytes, &tmap_b, leader_full, kb * BK, n0, hint_b);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -195,8 +200,10 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     uint32_t it = 0;
     for (int t = first_tile; t < num_tiles; t += tile_step, ++it) {
       const uint32_t acc = it & 1u, acc_phase = (it >> 1) & 1u;
-      const int m0 = (t % p.tiles_m) * kBM2 + (int)cta_rank * 128;
-      const int n0 = p.n_begin + (t / p.tiles_m) * kBN2;
+      int tm, tn;
+      tile_coords(p, t, tm, tn);
+      const int m0 = tm * kBM2 + (int)cta_rank * 128;
+      const int n0 = p.n_begin + tn * kBN2;
       if (!mbar_wait_bounded(&tmem_full[acc], acc_phase, abort_flag)) break;
       tc_fence_after();
       epilogue_tile<kBN2>(p, tmem_base + acc * kBN2 + ((uint32_t)(quad * 32) << 16),
@@ -220,6 +227,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 }
 
 constexpr int kStages2 = 6;
+void choose_tile_order(GemmParams& p, const liger_gemm_args& a, int tile_m, int tile_n);
 
 // Launches the 2-CTA kernel.  Returns LIGER_ERR_UNSUPPORTED (without touching the error text) when
 // this shape is better served by the 1-CTA kernel.
@@ -229,6 +237,7 @@ int launch_gemm_2cta(const liger_gemm_args& a, const GemmParams& p0, int sm_coun
   p.tiles_m = (a.m + kBM2 - 1) / kBM2;
   p.tiles_n = (a.n_end - a.n_begin + kBN2 - 1) / kBN2;
   p.kblocks = (a.k + BK - 1) / BK;
+  choose_tile_order(p, a, kBM2, kBN2);
   const int tiles = p.tiles_m * p.tiles_n;
   static int max_clusters = -1;
   LIGER_CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_2cta_kernel<kStages2>, cudaFuncAttributeMaxDynamicSharedMemorySize,

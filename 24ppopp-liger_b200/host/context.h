@@ -91,6 +91,8 @@ struct COMM_ARGS {
   liger_comm* comm = nullptr;
   int channel = 0;
   size_t partial_off = 0, out_off = 0;
+  size_t recv_off = 0;  // receive slots of the copy-engine variant
+  int copy_engine = 0;  // 1: liger_allreduce_ce instead of liger_allreduce_fused
   const void* residual_in = nullptr;
   void* hidden = nullptr;
   const void* bias = nullptr;

@@ -113,6 +113,10 @@ inline FuncWrap make_comm(int name, float placeholder_ms, const COMM_ARGS& c) {
   COMM_ARGS copy = c;
   return FuncWrap(name, placeholder_ms, COMMUNICATION,
                   [copy](const DynamicNvInitParam& d) {
+                    if (copy.copy_engine)
+                      return liger_allreduce_ce(copy.comm, copy.channel, copy.partial_off, copy.recv_off, copy.out_off,
+                                                copy.residual_in, copy.hidden, copy.bias, copy.gamma, copy.beta, copy.m,
+                                                copy.n, copy.row_begin, copy.row_end, d.stream);
                     return liger_allreduce_fused(copy.comm, copy.channel, copy.partial_off, copy.out_off,
                                                  copy.residual_in, copy.hidden, copy.bias, copy.gamma, copy.beta,
                                                  copy.m, copy.n, copy.row_begin, copy.row_end, copy.one_shot, d.stream);
@@ -154,7 +158,7 @@ struct Workspace {
   half_t* attn = nullptr;     // [M, h*D]
   half_t* act = nullptr;      // [M, F/ws]
   float* decode_scratch = nullptr;
-  size_t partial_off = 0, normed_off = 0, xbuf_off = 0;  // byte offsets inside the comm data region
+  size_t partial_off = 0, normed_off = 0, xbuf_off = 0, recv_off = 0;  // byte offsets inside the comm data region
 };
 
 // What follows an all-reduce (or, with world_size == 1, the row-parallel GEMM): an optional
@@ -223,7 +227,7 @@ class Bert_MHA {
       if (ws == 1 && post.residual_in) {  // no all-reduce to fuse the residual into: use the epilogue
         a.epilogue = LIGER_EPI_RESIDUAL; a.bias = post.bias; a.residual = post.residual_in; a.ldr = n;
         a.c = w.hidden;
-      } else if (ws > 1 && !is_one_shot(M, n)) {  // reduce-scatter by the epilogue's own stores
+      } else if (ws > 1 && !is_one_shot(M, n) && !use_copy_engines()) {  // reduce-scatter by the epilogue's own stores
         a.epilogue = LIGER_EPI_SCATTER; a.scatter_comm = SParam.comm; a.scatter_off = w.partial_off;
       }
       vec.push_back(make_gemm(2, 2.0f, a));
@@ -258,7 +262,7 @@ class Bert_MHA {
       GEMM_ARGS a = linear_w_row->args(w.attn, w.partial, M);
       if (ws == 1 && post.residual_in) {
         a.epilogue = LIGER_EPI_RESIDUAL; a.bias = post.bias; a.residual = post.residual_in; a.ldr = n; a.c = w.hidden;
-      } else if (ws > 1 && !is_one_shot(M, n)) {
+      } else if (ws > 1 && !is_one_shot(M, n) && !use_copy_engines()) {
         a.epilogue = LIGER_EPI_SCATTER; a.scatter_comm = SParam.comm; a.scatter_off = w.partial_off;
       }
       vec.push_back(make_gemm(2, 2.0f, a));
@@ -277,6 +281,7 @@ class Bert_MHA {
       c.comm = sp.comm; c.channel = sh.slot; c.partial_off = w.partial_off; c.out_off = post.out_off;
       c.m = M; c.n = n; c.row_begin = 0; c.row_end = M;
       c.one_shot = is_one_shot(M, n) ? 1 : 3;
+      if (!is_one_shot(M, n) && use_copy_engines()) { c.copy_engine = 1; c.recv_off = w.recv_off; }
       if (post.residual_in) { c.residual_in = post.residual_in; c.hidden = w.hidden; c.bias = post.bias; }
       c.gamma = post.gamma; c.beta = post.beta;
       return make_comm(name, 2.0f, c);
@@ -289,6 +294,13 @@ class Bert_MHA {
   }
   // payloads up to 1 MiB (decode) are latency bound: every rank reduces everything itself
   static bool is_one_shot(int M, int n) { return (size_t)M * n * 2 <= ((size_t)1 << 20); }
+  // LIGER_COMM_MODE=ce moves the inter-GPU traffic of the two-shot collective to the copy engines
+  // (liger_allreduce_ce); the default keeps it in the kernels (GEMM epilogue scatter + fused all-reduce).
+  static bool use_copy_engines() {
+    static int v = -1;
+    if (v < 0) { const char* e = getenv("LIGER_COMM_MODE"); v = (e && std::string(e) == "ce") ? 1 : 0; }
+    return v == 1;
+  }
 };
 
 // ---- MLP block: kernels 4-6 (src/layer/bert_layer.h:19-63) --------------------------------------------
@@ -329,7 +341,7 @@ class Bert_MLP {
       if (ws == 1 && post.residual_in) {
         a.epilogue = LIGER_EPI_RESIDUAL; a.bias = post.bias; a.residual = post.residual_in; a.ldr = n;
         a.c = post.direct_out ? post.direct_out : (void*)w.hidden;
-      } else if (ws > 1 && !Bert_MHA::is_one_shot(M, n)) {
+      } else if (ws > 1 && !Bert_MHA::is_one_shot(M, n) && !Bert_MHA::use_copy_engines()) {
         a.epilogue = LIGER_EPI_SCATTER; a.scatter_comm = SParam.comm; a.scatter_off = w.partial_off;
       }
       vec.push_back(make_gemm(5, 2.0f, a));
@@ -394,7 +406,7 @@ class Bert_Model {
   static size_t comm_bytes_needed(const BertInitParam& bp) {
     // + kMaxRanks rows: the scattered layout [ws][ceil(M/ws)][H] can exceed M rows by up to ws - 1
     const size_t mh = round_up(((size_t)bp.max_batch_size * bp.max_seq_len + LIGER_COMM_MAX_RANKS) * bp.hidden() * 2, 256);
-    return 3 * mh * (size_t)(bp.workspace_slots > 0 ? bp.workspace_slots : 1);
+    return 4 * mh * (size_t)(bp.workspace_slots > 0 ? bp.workspace_slots : 1);
   }
 
   // The flat kernel vector of one request: layer_num encoders back to back (src/layer/bert.h:104-115).
@@ -586,14 +598,15 @@ class Bert_Model {
     const int nslots = BertParams.workspace_slots > 0 ? BertParams.workspace_slots : 1;
     uint8_t* sym = nullptr;
     if (ws > 1) {
-      if (liger_comm_data_bytes(SParam.comm) < 3 * mh * nslots)
+      if (liger_comm_data_bytes(SParam.comm) < 4 * mh * nslots)
         throw std::runtime_error("Bert_Model: communicator data region smaller than comm_bytes_needed()");
       sym = (uint8_t*)liger_comm_data(SParam.comm);
     }
     for (int s = 0; s < nslots; ++s) {
       Workspace w;
       if (ws > 1) {
-        w.partial_off = (size_t)s * 3 * mh; w.normed_off = w.partial_off + mh; w.xbuf_off = w.normed_off + mh;
+        w.partial_off = (size_t)s * 4 * mh; w.normed_off = w.partial_off + mh; w.xbuf_off = w.normed_off + mh;
+        w.recv_off = w.xbuf_off + mh;
         w.partial = (half_t*)(sym + w.partial_off);
         w.normed = (half_t*)(sym + w.normed_off);
         w.xbuf = (half_t*)(sym + w.xbuf_off);

@@ -58,6 +58,9 @@ inline FuncWrap decompose_comm_callback(const FuncWrap& old_func, int factor, in
   c.row_end = slice_bound(c.m, ub + n, factor, 1);
   FuncWrap f(old_func.name, duration, COMMUNICATION,
              [c](const DynamicNvInitParam& d) {
+               if (c.copy_engine)
+                 return liger_allreduce_ce(c.comm, c.channel, c.partial_off, c.recv_off, c.out_off, c.residual_in, c.hidden,
+                                           c.bias, c.gamma, c.beta, c.m, c.n, c.row_begin, c.row_end, d.stream);
                return liger_allreduce_fused(c.comm, c.channel, c.partial_off, c.out_off, c.residual_in, c.hidden, c.bias,
                                             c.gamma, c.beta, c.m, c.n, c.row_begin, c.row_end, c.one_shot, d.stream);
              },

@@ -299,6 +299,20 @@ LIGER_API int liger_allreduce_fused(liger_comm* comm, int channel, size_t partia
                                     const void* beta, int m, int n, int row_begin, int row_end, int one_shot,
                                     void* stream);
 
+/*
+ * The same collective (two-shot, rows [row_begin, row_end)) with all inter-GPU data movement on the
+ * copy engines instead of SM loads / stores: peer copies deliver every rank's slice of the partials
+ * (plain [M, N] layout at partial_off) into the owners' receive slots ([world_size][rows][N] at
+ * recv_off), a small kernel reduces the owned rows from local memory (+ residual + LayerNorm) into
+ * the local [M, N] tensor at out_off, and peer copies distribute the finished rows; one-warp barrier
+ * kernels order the phases across ranks.  Meant for interleaved execution: the SMs stay free for the
+ * GEMMs of the other requests (or micro-batches) that run under the transfer.  Same arithmetic and
+ * summation order as liger_allreduce_fused.
+ */
+LIGER_API int liger_allreduce_ce(liger_comm* comm, int channel, size_t partial_off, size_t recv_off, size_t out_off,
+                                 const void* residual_in, void* hidden, const void* bias, const void* gamma,
+                                 const void* beta, int m, int n, int row_begin, int row_end, void* stream);
+
 /* ------------------------------------------------------------------------------------------ */
 /* The layer stack and the serving entry points                                               */
 /* ------------------------------------------------------------------------------------------ */
