@@ -40,17 +40,23 @@ __device__ __forceinline__ int swz(int row, int col) {
   return row * D + ((((col >> 3) ^ (row & 7)) << 3) | (col & 7));
 }
 
-// copy a [64][D] tile (rows r0.. of a [nrows][D] matrix, zero-filled past nrows) into shared memory
+// asynchronous copy of a [64][D] tile (rows r0.. of a [nrows][D] matrix, zero-filled past nrows) into
+// shared memory: 16-byte cp.async per chunk, completion tracked by the caller's commit / wait groups
 template <int D>
-__device__ __forceinline__ void load_tile(__half* s, const __half* __restrict__ g, int r0, int nrows) {
+__device__ __forceinline__ void load_tile_async(__half* s, const __half* __restrict__ g, int r0, int nrows) {
   constexpr int CPR = D / 8;
   for (int i = threadIdx.x; i < 64 * CPR; i += kAttnThreads) {
     const int r = i / CPR, c = i % CPR;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (r0 + r < nrows) v = __ldg(reinterpret_cast<const uint4*>(g + (size_t)(r0 + r) * D + c * 8));
-    *reinterpret_cast<uint4*>(s + swz<D>(r, c * 8)) = v;
+    const bool ok = r0 + r < nrows;
+    const __half* src = ok ? g + (size_t)(r0 + r) * D + c * 8 : g;
+    const uint32_t dst = smem_u32(s + swz<D>(r, c * 8));
+    const int bytes = ok ? 16 : 0;  // src-size 0: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
   }
 }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 template <int D>
 __global__ void __launch_bounds__(kAttnThreads)
@@ -59,8 +65,8 @@ attention_prefill_kernel(const __half* __restrict__ q, const __half* __restrict_
                          float scale, int causal) {
   extern __shared__ __align__(16) uint8_t smem_attn[];
   __half* sQ = reinterpret_cast<__half*>(smem_attn);
-  __half* sK = sQ + kBr * D;
-  __half* sV = sK + kBc * D;
+  __half* sKbuf = sQ + kBr * D;           // two K stages
+  __half* sVbuf = sKbuf + 2 * kBc * D;    // two V stages
 
   const int q0 = blockIdx.x * kBr;
   const int head = blockIdx.y;
@@ -72,7 +78,17 @@ attention_prefill_kernel(const __half* __restrict__ q, const __half* __restrict_
   const __half* kg = k + bh;
   const __half* vg = v + bh;
 
-  load_tile<D>(sQ, qg, q0, S);
+  int nblocks = (S + kBc - 1) / kBc;
+  if (causal && mask == nullptr) {
+    const int last = (q0 + kBr - 1) / kBc + 1;  // blocks past the diagonal contribute exp(-10000 - max) == 0
+    if (last < nblocks) nblocks = last;
+  }
+  // prologue: Q and the first K/V block in flight together
+  load_tile_async<D>(sQ, qg, q0, S);
+  load_tile_async<D>(sKbuf, kg, 0, S);
+  load_tile_async<D>(sVbuf, vg, 0, S);
+  cp_async_commit();
+  cp_async_wait<0>();
   __syncthreads();
 
   // Q fragments for this warp's 16 rows
@@ -90,17 +106,20 @@ attention_prefill_kernel(const __half* __restrict__ q, const __half* __restrict_
   float m_run[2] = {-INFINITY, -INFINITY};
   float l_run[2] = {0.0f, 0.0f};
 
-  int nblocks = (S + kBc - 1) / kBc;
-  if (causal && mask == nullptr) {
-    const int last = (q0 + kBr - 1) / kBc + 1;  // blocks past the diagonal contribute exp(-10000 - max) == 0
-    if (last < nblocks) nblocks = last;
-  }
-
   for (int jb = 0; jb < nblocks; ++jb) {
-    __syncthreads();  // previous block's K/V fully consumed
-    load_tile<D>(sK, kg, jb * kBc, S);
-    load_tile<D>(sV, vg, jb * kBc, S);
-    __syncthreads();
+    // double buffering: block jb sits in stage jb & 1; start fetching block jb + 1 into the other stage
+    // (every warp finished reading that stage at the barrier that ended iteration jb - 1)
+    const __half* sK = sKbuf + (jb & 1) * kBc * D;
+    const __half* sV = sVbuf + (jb & 1) * kBc * D;
+    if (jb + 1 < nblocks) {
+      load_tile_async<D>(sKbuf + ((jb + 1) & 1) * kBc * D, kg, (jb + 1) * kBc, S);
+      load_tile_async<D>(sVbuf + ((jb + 1) & 1) * kBc * D, vg, (jb + 1) * kBc, S);
+    }
+    cp_async_commit();
+    if (jb > 0) {
+      cp_async_wait<1>();  // everything but the group just committed has landed: block jb is complete
+      __syncthreads();
+    }
 
     float s[kBc / 8][4];
 #pragma unroll
@@ -183,7 +202,9 @@ attention_prefill_kernel(const __half* __restrict__ q, const __half* __restrict_
         mma_16816(o[2 * dp + 1], pf, vf[2], vf[3]);
       }
     }
+    __syncthreads();  // all warps are done with stage jb & 1 before iteration jb + 1 refills it
   }
+  cp_async_wait<0>();
 
   // normalise: p = exp(t - max) / (sum + 1e-6)   (src/cuda/attention_kernels.cu:567-568)
 #pragma unroll
@@ -321,7 +342,7 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ scratch,
 template <int D>
 static int launch_prefill(const void* q, const void* k, const void* v, const void* mask, void* out, int batch, int heads,
                           int S, int ldo, float scale, int causal, cudaStream_t stream) {
-  const int smem = (kBr + 2 * kBc) * D * 2;
+  const int smem = (kBr + 4 * kBc) * D * 2;
   LIGER_CUDA_TRY(cudaFuncSetAttribute(attention_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   dim3 grid((S + kBr - 1) / kBr, heads, batch);
   attention_prefill_kernel<D><<<grid, kAttnThreads, smem, stream>>>((const __half*)q, (const __half*)k, (const __half*)v,
