@@ -201,15 +201,22 @@ static int launch_gemm(const liger_gemm_args& a, const GemmParams& p0, int sm_co
 // the panels cut DRAM traffic: the kernel is limited by power and the tensor pipe, not by DRAM.  The panel
 // orders stay selectable (LIGER_GEMM_ORDER = 1: panels, 2: panels + hints) for other shapes.
 void choose_tile_order(GemmParams& p, const liger_gemm_args& a, int tile_m, int tile_n) {
-  static int order = -1;
-  if (order < 0) { const char* e = getenv("LIGER_GEMM_ORDER"); order = e ? atoi(e) : 0; }
-  p.use_hints = order == 2 ? 1 : 0;
+  static int order = -1, hints = -1;
+  static double cap = 0.0;
+  if (order < 0) {
+    const char* e = getenv("LIGER_GEMM_ORDER");
+    order = e ? atoi(e) : 0;
+    e = getenv("LIGER_GEMM_HINTS");
+    hints = e ? atoi(e) : (order == 2 ? 1 : 0);
+    e = getenv("LIGER_GEMM_PANEL_MB");
+    cap = (e ? atof(e) : 56.0) * 1e6;  // bytes of L2 a resident panel may take
+  }
+  p.use_hints = hints;
   if (order == 0) {  // plain m-fastest order over the whole matrix
     p.stationary = 0;
     p.panel_tiles = p.tiles_m;
     return;
   }
-  const double cap = 56.0e6;  // bytes of L2 a resident panel may take (about half of the 126 MB L2)
   const double row_bytes = 2.0 * a.k;
   const double a_bytes = (double)a.m * row_bytes, b_bytes = (double)(a.n_end - a.n_begin) * row_bytes;
   const int pa = (int)ceil(a_bytes / cap), pb = (int)ceil(b_bytes / cap);
@@ -220,7 +227,6 @@ void choose_tile_order(GemmParams& p, const liger_gemm_args& a, int tile_m, int 
     int t = rows / tile_m;
     if (t < 1) t = 1;
     p.panel_tiles = t > p.tiles_m ? p.tiles_m : t;
-    // balance the panels: same number of panels, equal sizes
     const int panels = (p.tiles_m + p.panel_tiles - 1) / p.panel_tiles;
     p.panel_tiles = (p.tiles_m + panels - 1) / panels;
   } else {
