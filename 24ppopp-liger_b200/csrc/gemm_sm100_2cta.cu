@@ -9,6 +9,8 @@
 // Barriers: `full[s]` lives in the leader (cluster rank 0); both CTAs' TMA loads signal it.
 // `empty[s]` and `tmem_full[a]` exist in both CTAs and are signalled together by the leader's
 // tcgen05.commit; `tmem_empty[a]` lives in the leader and collects 4 + 4 epilogue-warp arrivals.
+#include <cstdlib>
+
 #include "gemm_epilogue.cuh"
 
 namespace liger {
@@ -226,11 +228,186 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   if (threadIdx.x == 0 && *abort_flag) report_failure(p.status, LIGER_DEV_TIMEOUT, 0x110u, blockIdx.x, 0);
 }
 
+// ---- wide variant: one 256x512 tile per CTA pair -----------------------------------------------------
+// Both TMEM accumulators of a CTA belong to the same tile (column halves [0,256) and [256,512)), so
+// every A tile fetched into shared memory feeds twice as many MMAs: 48 KB of operands per k-block
+// and CTA for 128x512 outputs instead of 32 KB for 128x256, i.e. 25 % less L2 and shared-memory
+// traffic and about 40 % less DRAM traffic per FLOP.  The price: the epilogue of a tile overlaps only
+// the first half of the next tile's start (half h is handed back as soon as it is drained), so the
+// variant is used for long K only, where the tile's MMA time dwarfs the epilogue.
+template <int STAGES>
+struct Gemm2WideCfg {
+  static constexpr int kABytes = 128 * BK * 2;
+  static constexpr int kBBytes = 2 * 128 * BK * 2;  // this CTA's 128 rows of each column half
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kEpiBytesPerWarp = 32 * 128 * 2;
+  static constexpr int kEpiBytes = 4 * kEpiBytesPerWarp;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kSmemBytes = STAGES * kStageBytes + kEpiBytes + kBarrierBytes + 1024;
+  static constexpr int kTmemCols = 512;
+};
+constexpr int kBNW = 512;
+
+template <int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_2cta_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                              const GemmParams p) {
+  using Cfg = Gemm2WideCfg<STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* epi_stage = smem + STAGES * Cfg::kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(epi_stage + Cfg::kEpiBytes);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full = empty_bar + STAGES;   // [2]: one per column half
+  uint64_t* tmem_empty = tmem_full + 2;       // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_ctarank();
+  const bool leader = cta_rank == 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 8);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int first_tile = (int)cluster_id_x();
+  const int tile_step = (int)num_clusters_x();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
+        int tm, tn;
+        tile_coords(p, t, tm, tn);
+        const int m0 = tm * kBM2 + (int)cta_rank * 128;
+        const int n0 = p.n_begin + tn * kBNW + (int)cta_rank * 128;
+        for (int kb = 0; kb < p.kblocks; ++kb) {
+          if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+          uint8_t* sa = smem + stage * Cfg::kStageBytes;
+          const uint32_t leader_full = smem_u32(&full_bar[stage]) & 0xFEFFFFFFu;
+          if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);
+          tma_load_2d_pair(sa, &tmap_a, leader_full, kb * BK, m0, kL2EvictNormal);
+          tma_load_2d_pair(sa + Cfg::kABytes, &tmap_b, leader_full, kb * BK, n0, kL2EvictNormal);
+          tma_load_2d_pair(sa + Cfg::kABytes + 128 * BK * 2, &tmap_b, leader_full, kb * BK, n0 + 256, kL2EvictNormal);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(kBM2, 256);
+      uint32_t stage = 0, phase = 0, it = 0;
+      bool ok = true;
+      for (int t = first_tile; t < num_tiles && ok; t += tile_step, ++it) {
+        const uint32_t tphase = it & 1u;
+        for (int kb = 0; kb < p.kblocks && ok; ++kb) {
+          if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint64_t da = make_sw128_kmajor_desc(sa);
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            if (kb == 0) {  // the previous tile's epilogue must have drained this half
+              if (!mbar_wait_bounded(&tmem_empty[h], tphase ^ 1u, abort_flag)) { ok = false; break; }
+              tc_fence_after();
+            }
+            const uint64_t db = make_sw128_kmajor_desc(sa + Cfg::kABytes + h * 128 * BK * 2);
+#pragma unroll
+            for (int k4 = 0; k4 < BK / 16; ++k4)
+              umma_f16_pair(tmem_base + h * 256, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc,
+                            (kb | k4) != 0 ? 1u : 0u);
+          }
+          if (!ok) break;
+          umma_commit_pair(&empty_bar[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) { umma_commit_pair(&tmem_full[0]); umma_commit_pair(&tmem_full[1]); }
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const uint32_t leader_tmem_empty0 = map_to_cta(smem_u32(&tmem_empty[0]), 0);
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = first_tile; t < num_tiles && ok; t += tile_step, ++it) {
+      const uint32_t tphase = it & 1u;
+      int tm, tn;
+      tile_coords(p, t, tm, tn);
+      const int m0 = tm * kBM2 + (int)cta_rank * 128;
+      const int n0 = p.n_begin + tn * kBNW;
+      for (int h = 0; h < 2; ++h) {
+        if (!mbar_wait_bounded(&tmem_full[h], tphase, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        epilogue_tile<256>(p, tmem_base + h * 256 + ((uint32_t)(quad * 32) << 16),
+                           epi_stage + (warp - 2) * Cfg::kEpiBytesPerWarp, m0 + quad * 32, n0 + h * 256, lane);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(leader_tmem_empty0 + h * 8u);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    __syncwarp();
+    tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+  }
+  if (threadIdx.x == 0 && *abort_flag) report_failure(p.status, LIGER_DEV_TIMEOUT, 0x120u, blockIdx.x, 0);
+}
+
 constexpr int kStages2 = 6;
+constexpr int kStagesWide = 4;
+
 void choose_tile_order(GemmParams& p, const liger_gemm_args& a, int tile_m, int tile_n);
 
 // Launches the 2-CTA kernel.  Returns LIGER_ERR_UNSUPPORTED (without touching the error text) when
 // this shape is better served by the 1-CTA kernel.
+static int launch_gemm_2cta_wide(const liger_gemm_args& a, const GemmParams& p0, int max_clusters, cudaStream_t stream) {
+  using Cfg = Gemm2WideCfg<kStagesWide>;
+  GemmParams p = p0;
+  p.tiles_m = (a.m + kBM2 - 1) / kBM2;
+  p.tiles_n = (a.n_end - a.n_begin + kBNW - 1) / kBNW;
+  p.kblocks = (a.k + BK - 1) / BK;
+  choose_tile_order(p, a, kBM2, kBNW);
+  const int tiles = p.tiles_m * p.tiles_n;
+  LIGER_CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_2cta_wide_kernel<kStagesWide>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Cfg::kSmemBytes));
+  const int clusters = tiles < max_clusters ? tiles : max_clusters;
+  CUtensorMap tm_a, tm_b;
+  int rc;
+  if ((rc = make_tmap_2d_f16(&tm_a, a.a, (uint64_t)a.k, (uint64_t)a.m, (uint64_t)a.lda, BK, 128)) != LIGER_OK) return rc;
+  if ((rc = make_tmap_2d_f16(&tm_b, a.wt, (uint64_t)a.k, (uint64_t)a.n, (uint64_t)a.ldw, BK, 128)) != LIGER_OK) return rc;
+  gemm_tcgen05_2cta_wide_kernel<kStagesWide><<<2 * clusters, kGemmThreads, Cfg::kSmemBytes, stream>>>(tm_a, tm_b, p);
+  return check_launch("gemm_tcgen05_2cta_wide_kernel");
+}
+
 int launch_gemm_2cta(const liger_gemm_args& a, const GemmParams& p0, int sm_count, cudaStream_t stream) {
   using Cfg = Gemm2Cfg<kStages2>;
   GemmParams p = p0;
@@ -260,6 +437,16 @@ int launch_gemm_2cta(const liger_gemm_args& a, const GemmParams& p0, int sm_coun
     max_clusters = n;
   }
   if (max_clusters < 1) return LIGER_ERR_UNSUPPORTED;
+  {
+    // 256x512 tiles for long K when they still fill the machine at least as evenly as 256x256 ones:
+    // compare waves x tile width (LIGER_GEMM_WIDE = 0 / 1 forces the choice)
+    static int wide_env = -2;
+    if (wide_env == -2) { const char* e = getenv("LIGER_GEMM_WIDE"); wide_env = e ? atoi(e) : -1; }
+    const long tiles_w = (long)p.tiles_m * ((a.n_end - a.n_begin + kBNW - 1) / kBNW);
+    const long waves_w = (tiles_w + max_clusters - 1) / max_clusters, waves_n = ((long)tiles + max_clusters - 1) / max_clusters;
+    const bool geom_ok = a.k >= 8192 && tiles_w >= max_clusters && waves_w * 2 <= waves_n + (waves_n + 9) / 10;
+    if (wide_env == 1 || (wide_env < 0 && geom_ok)) return launch_gemm_2cta_wide(a, p0, max_clusters, stream);
+  }
   const int clusters = tiles < max_clusters ? tiles : max_clusters;
   CUtensorMap tm_a, tm_b;
   int rc;
