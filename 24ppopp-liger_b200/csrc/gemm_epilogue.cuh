@@ -29,6 +29,9 @@ struct GemmParams {
   uint8_t* peer[kMaxRanks];
   size_t scatter_off;
   int rank, rows_per_rank;
+  // 256x512 kernel: tiles [tail_start, tiles) form the last, partly filled wave; with tail_split they
+  // run as 256x256 halves, one per CTA pair, which ends that wave in half the time
+  int tail_start, tail_split;
   DeviceStatus* status;
 };
 
@@ -234,6 +237,217 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
       stage_writeout<W>(p, stage, row0, pcol0, p.n_end, lane);
     }
     __syncwarp();  // the staging tile is reused by the next pass
+  }
+}
+
+// ---- pipelined epilogue ------------------------------------------------------------------------------
+// Used where the epilogue is not hidden behind the next tile's MMAs (the 256x512 kernel, whose tile
+// owns all of TMEM).  Differences from epilogue_tile: the TMEM load (and the residual load) of unit
+// u+1 is in flight while unit u is converted; the bias is read once per tile (8 columns per lane,
+// before the accumulator is ready) and handed round by shuffles; destination addresses are split into a per-lane column part computed once
+// per pass and a row part advanced without divisions.
+
+// tcgen05.wait::ld that also names the loaded registers, so that no use of them can be scheduled
+// ahead of the wait.
+__device__ __forceinline__ void tmem_ld_wait_regs(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                 "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                 "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
+
+// Staged [32 x 64] output tile -> global memory; a warp instruction stores 4 rows of 128 contiguous bytes.
+template <int EPI>
+__device__ __forceinline__ void stage_writeout64(const GemmParams& p, uint8_t* stage, int row0, int out_col0, int out_end,
+                                                 int lane) {
+  const int ch = lane & 7, rsub = lane >> 3;
+  const int col = out_col0 + ch * 8;
+  if (col >= out_end) return;
+  int row = row0 + rsub;
+  if constexpr (EPI == LIGER_EPI_QKV_SPLIT) {
+    const int hd = p.heads * p.head_dim;
+    const int which = col / hd;
+    const int rem = col - which * hd;
+    const int head = rem / p.head_dim;
+    const int d = rem - head * p.head_dim;
+    const bool cache = which != 0 && p.kv_stride > 0;
+    const size_t S = cache ? (size_t)p.kv_stride : (size_t)p.seq_len;
+    __half* base = (which == 0 ? p.qkv[0] : which == 1 ? p.qkv[1] : p.qkv[2]) +
+                   ((size_t)head * S + (cache ? (size_t)p.kv_pos : 0)) * p.head_dim + d;
+    int b = row / p.seq_len, s = row - b * p.seq_len;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (row < p.m)
+        *reinterpret_cast<uint4*>(base + ((size_t)b * p.heads * S + (size_t)s) * p.head_dim) =
+            *stage_slot<64>(stage, rsub + i * 4, ch);
+      row += 4;
+      s += 4;
+      while (s >= p.seq_len) { s -= p.seq_len; ++b; }
+    }
+  } else if constexpr (EPI == LIGER_EPI_SCATTER) {
+    int owner = row / p.rows_per_rank, lr = row - owner * p.rows_per_rank;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (row < p.m)
+        *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.peer[owner] + p.scatter_off) +
+                                  (size_t)(p.rank * p.rows_per_rank + lr) * p.ldc + col) =
+            *stage_slot<64>(stage, rsub + i * 4, ch);
+      row += 4;
+      lr += 4;
+      while (lr >= p.rows_per_rank) { lr -= p.rows_per_rank; ++owner; }
+    }
+  } else {
+    __half* dst = p.c + (size_t)row * p.ldc + col;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (row < p.m) *reinterpret_cast<uint4*>(dst) = *stage_slot<64>(stage, rsub + i * 4, ch);
+      row += 4;
+      dst += (size_t)4 * p.ldc;
+    }
+  }
+}
+
+// Lane j of the warp holds the bias of columns [8j, 8j+8) of the warp's 256-column range.
+__device__ __forceinline__ uint4 bias_group(const uint4& bias8, int group) {
+  uint4 b;
+  b.x = __shfl_sync(0xffffffffu, bias8.x, group);
+  b.y = __shfl_sync(0xffffffffu, bias8.y, group);
+  b.z = __shfl_sync(0xffffffffu, bias8.z, group);
+  b.w = __shfl_sync(0xffffffffu, bias8.w, group);
+  return b;
+}
+
+// 32 accumulator columns of one row (columns [cl, cl+32) of the warp's range) + bias [+ residual /
+// GELU] -> 32 fp16 values
+template <int EPI>
+__device__ __forceinline__ void unit_math(const uint4& bias8, int cl, const uint32_t (&r)[32], const uint4 (&res)[4],
+                                          uint4 (&o)[4]) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    float v[8], b[8];
+    unpack8(bias_group(bias8, (cl >> 3) + g), b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]) + b[i];
+    if constexpr (EPI == LIGER_EPI_GELU) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = gelu_tanh(v[i]);
+    } else if constexpr (EPI == LIGER_EPI_RESIDUAL) {
+      unpack8(res[g], b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] += b[i];
+    }
+    o[g].x = pack_half2(v[0], v[1]);
+    o[g].y = pack_half2(v[2], v[3]);
+    o[g].z = pack_half2(v[4], v[5]);
+    o[g].w = pack_half2(v[6], v[7]);
+  }
+}
+
+__device__ __forceinline__ void unit_math_geglu(const uint4& bias8, int cl, const uint32_t (&gt)[32],
+                                                const uint32_t (&up)[32], uint4 (&o)[4]) {
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    float gv[8], uv[8], b[8];
+    unpack8(bias_group(bias8, (cl >> 3) + q), b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) gv[i] = __uint_as_float(gt[q * 8 + i]) + b[i];
+    unpack8(bias_group(bias8, (cl >> 3) + 4 + q), b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) uv[i] = __uint_as_float(up[q * 8 + i]) + b[i];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) gv[i] = gelu_tanh(gv[i]) * uv[i];
+    o[q].x = pack_half2(gv[0], gv[1]);
+    o[q].y = pack_half2(gv[2], gv[3]);
+    o[q].z = pack_half2(gv[4], gv[5]);
+    o[q].w = pack_half2(gv[6], gv[7]);
+  }
+}
+
+// Bias of columns [n0 + 8*lane, +8) (zeros past n_end or without a bias vector).
+__device__ __forceinline__ uint4 epilogue_bias8(const GemmParams& p, int n0, int lane) {
+  const int col = n0 + lane * 8;
+  if (p.bias == nullptr || col >= p.n_end) return make_uint4(0u, 0u, 0u, 0u);
+  return __ldg(reinterpret_cast<const uint4*>(p.bias + col));
+}
+
+// One warp's share of an accumulator: TMEM lanes [taddr.lane, +32) x 256 columns starting at
+// accumulator column n0 -> rows [row0, row0+32).  `stage` is the warp's [32 x 64] staging tile,
+// `bias8` this lane's 8 bias values (see epilogue_bias8).
+template <int EPI>
+__device__ __forceinline__ void epilogue_warp_pipelined(const GemmParams& p, uint32_t taddr, uint8_t* stage,
+                                                        const uint4& bias8, int row0, int n0, int lane) {
+  if (n0 >= p.n_end) return;
+  const int row = row0 + lane;
+  if constexpr (EPI == LIGER_EPI_GEGLU) {
+    // unit = 32 gate + 32 value columns -> 32 outputs; two units fill the staging tile
+    const int nu = min(4, (p.n_end - n0 + 63) / 64);
+    uint32_t g0[32], u0[32], g1[32], u1[32];
+    tmem_ld_32x32(taddr, g0);
+    tmem_ld_32x32(taddr + 32, u0);
+#pragma unroll 1
+    for (int u = 0; u < nu; u += 2) {
+      uint4 o[4];
+      tmem_ld_wait_regs(g0);
+      tmem_ld_wait_regs(u0);
+      if (u + 1 < nu) {
+        tmem_ld_32x32(taddr + (u + 1) * 64, g1);
+        tmem_ld_32x32(taddr + (u + 1) * 64 + 32, u1);
+      }
+      unit_math_geglu(bias8, u * 64, g0, u0, o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) *stage_slot<64>(stage, lane, j) = o[j];
+      if (u + 1 < nu) {
+        tmem_ld_wait_regs(g1);
+        tmem_ld_wait_regs(u1);
+        if (u + 2 < nu) {
+          tmem_ld_32x32(taddr + (u + 2) * 64, g0);
+          tmem_ld_32x32(taddr + (u + 2) * 64 + 32, u0);
+        }
+        unit_math_geglu(bias8, (u + 1) * 64, g1, u1, o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) *stage_slot<64>(stage, lane, 4 + j) = o[j];
+      }
+      __syncwarp();
+      stage_writeout64<EPI>(p, stage, row0, (n0 + u * 64) >> 1, p.n_end >> 1, lane);
+      __syncwarp();
+    }
+  } else {
+    const int nu = min(8, (p.n_end - n0 + 31) / 32);
+    const __half* res_row = nullptr;
+    if constexpr (EPI == LIGER_EPI_RESIDUAL) res_row = p.residual + (size_t)(row < p.m ? row : 0) * p.ldr + n0;
+    uint32_t r0[32], r1[32];
+    uint4 q0[4] = {}, q1[4] = {};
+    auto fetch = [&](int u, uint32_t (&r)[32], uint4 (&q)[4]) {
+      tmem_ld_32x32(taddr + u * 32, r);
+      if constexpr (EPI == LIGER_EPI_RESIDUAL) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+          if (n0 + u * 32 + g * 8 < p.n_end) q[g] = __ldg(reinterpret_cast<const uint4*>(res_row + u * 32 + g * 8));
+      }
+    };
+    fetch(0, r0, q0);
+#pragma unroll 1
+    for (int u = 0; u < nu; u += 2) {
+      uint4 o[4];
+      tmem_ld_wait_regs(r0);
+      if (u + 1 < nu) fetch(u + 1, r1, q1);
+      unit_math<EPI>(bias8, u * 32, r0, q0, o);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) *stage_slot<64>(stage, lane, j) = o[j];
+      if (u + 1 < nu) {
+        tmem_ld_wait_regs(r1);
+        if (u + 2 < nu) fetch(u + 2, r0, q0);
+        unit_math<EPI>(bias8, (u + 1) * 32, r1, q1, o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) *stage_slot<64>(stage, lane, 4 + j) = o[j];
+      }
+      __syncwarp();
+      stage_writeout64<EPI>(p, stage, row0, n0 + u * 32, p.n_end, lane);
+      __syncwarp();
+    }
   }
 }
 

@@ -98,7 +98,8 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
                : "memory");
 }
 
-template <int STAGES>
+// EPI: the epilogue kind, a template parameter so that each kind gets its own register allocation.
+template <int STAGES, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          const GemmParams p) {
@@ -206,10 +207,11 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       tile_coords(p, t, tm, tn);
       const int m0 = tm * kBM2 + (int)cta_rank * 128;
       const int n0 = p.n_begin + tn * kBN2;
+      const uint4 bias8 = epilogue_bias8(p, n0, lane);  // in flight while the MMAs finish
       if (!mbar_wait_bounded(&tmem_full[acc], acc_phase, abort_flag)) break;
       tc_fence_after();
-      epilogue_tile<kBN2>(p, tmem_base + acc * kBN2 + ((uint32_t)(quad * 32) << 16),
-                          epi_stage + (warp - 2) * Cfg::kEpiBytesPerWarp, m0 + quad * 32, n0, lane);
+      epilogue_warp_pipelined<EPI>(p, tmem_base + acc * kBN2 + ((uint32_t)(quad * 32) << 16),
+                                   epi_stage + (warp - 2) * Cfg::kEpiBytesPerWarp, bias8, m0 + quad * 32, n0, lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(leader_tmem_empty0 + acc * 8u);
@@ -232,24 +234,54 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
 // Both TMEM accumulators of a CTA belong to the same tile (column halves [0,256) and [256,512)), so
 // every A tile fetched into shared memory feeds twice as many MMAs: 48 KB of operands per k-block
 // and CTA for 128x512 outputs instead of 32 KB for 128x256, i.e. 25 % less L2 and shared-memory
-// traffic and about 40 % less DRAM traffic per FLOP.  The price: the epilogue of a tile overlaps only
-// the first half of the next tile's start (half h is handed back as soon as it is drained), so the
-// variant is used for long K only, where the tile's MMA time dwarfs the epilogue.
+// traffic and less than half the DRAM traffic per FLOP.  The price: a tile owns all of TMEM, so its
+// epilogue cannot hide behind the next tile's MMAs.  It is kept short instead -- eight epilogue warps
+// (four per column half, working at the same time) running the pipelined epilogue -- and the variant
+// is used for long K only, where the tile's MMA time dwarfs it.  Warps: 0 TMA producer, 1 MMA issuer
+// and TMEM owner, 2-5 epilogue of half 0, 6-9 epilogue of half 1.
+constexpr int kWideThreads = 320;
 template <int STAGES>
 struct Gemm2WideCfg {
   static constexpr int kABytes = 128 * BK * 2;
-  static constexpr int kBBytes = 2 * 128 * BK * 2;  // this CTA's 128 rows of each column half
-  static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kEpiBytesPerWarp = 32 * 128 * 2;
-  static constexpr int kEpiBytes = 4 * kEpiBytesPerWarp;
+  static constexpr int kBHalfBytes = 128 * BK * 2;  // this CTA's 128 rows of one column half
+  static constexpr int kStageBytes = kABytes + 2 * kBHalfBytes;
+  static constexpr int kEpiBytesPerWarp = 32 * 64 * 2;
+  static constexpr int kEpiBytes = 8 * kEpiBytesPerWarp;
   static constexpr int kBarrierBytes = 256;
   static constexpr int kSmemBytes = STAGES * kStageBytes + kEpiBytes + kBarrierBytes + 1024;
   static constexpr int kTmemCols = 512;
 };
 constexpr int kBNW = 512;
 
-template <int STAGES>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+// The it-th tile of a CTA pair: a whole 256x512 tile (halves = 2) or, in a split tail, one 256x256
+// half of one (halves = 1; it uses operand slot and accumulator 0).  n0 is the tile's first
+// accumulator column.  All warps of both CTAs evaluate this identically.
+struct WideTile {
+  int tm, n0, halves;
+};
+__device__ __forceinline__ bool wide_tile(const GemmParams& p, int cluster, int nclusters, int it, WideTile& w) {
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int t = cluster + it * nclusters;
+  int tn;
+  if (t < p.tail_start || !p.tail_split) {
+    if (t >= num_tiles) return false;
+    tile_coords(p, t, w.tm, tn);
+    w.n0 = p.n_begin + tn * kBNW;
+    w.halves = 2;
+    return true;
+  }
+  const int r = t - p.tail_start;  // tail_start is a multiple of nclusters: r == cluster in the tail wave
+  if (r >= 2 * (num_tiles - p.tail_start)) return false;
+  tile_coords(p, p.tail_start + (r >> 1), w.tm, tn);
+  w.n0 = p.n_begin + tn * kBNW + (r & 1) * 256;
+  w.halves = 1;
+  return true;
+}
+
+// One instantiation per epilogue kind: inlining all of them behind a run-time switch costs the
+// register allocator its footing (heavy spills); separately each fits without.
+template <int STAGES, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kWideThreads, 1)
 gemm_tcgen05_2cta_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                               const GemmParams p) {
   using Cfg = Gemm2WideCfg<STAGES>;
@@ -275,7 +307,7 @@ gemm_tcgen05_2cta_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
-      mbar_init(&tmem_empty[a], 8);
+      mbar_init(&tmem_empty[a], 8);  // 4 epilogue warps of this half x 2 CTAs
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -292,27 +324,27 @@ gemm_tcgen05_2cta_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int num_tiles = p.tiles_m * p.tiles_n;
-  const int first_tile = (int)cluster_id_x();
-  const int tile_step = (int)num_clusters_x();
+  const int cluster = (int)cluster_id_x();
+  const int nclusters = (int)num_clusters_x();
+  WideTile w;
 
   if (warp == 0) {
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int t = first_tile; t < num_tiles && ok; t += tile_step) {
-        int tm, tn;
-        tile_coords(p, t, tm, tn);
-        const int m0 = tm * kBM2 + (int)cta_rank * 128;
-        const int n0 = p.n_begin + tn * kBNW + (int)cta_rank * 128;
+      for (int it = 0; ok && wide_tile(p, cluster, nclusters, it, w); ++it) {
+        const int m0 = w.tm * kBM2 + (int)cta_rank * 128;
+        const int n0 = w.n0 + (int)cta_rank * 128;
+        const uint32_t tx = 2u * (uint32_t)(Cfg::kABytes + w.halves * Cfg::kBHalfBytes);
         for (int kb = 0; kb < p.kblocks; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
           const uint32_t leader_full = smem_u32(&full_bar[stage]) & 0xFEFFFFFFu;
-          if (leader) mbar_arrive_expect_tx(&full_bar[stage], 2 * Cfg::kStageBytes);
+          if (leader) mbar_arrive_expect_tx(&full_bar[stage], tx);
           tma_load_2d_pair(sa, &tmap_a, leader_full, kb * BK, m0, kL2EvictNormal);
           tma_load_2d_pair(sa + Cfg::kABytes, &tmap_b, leader_full, kb * BK, n0, kL2EvictNormal);
-          tma_load_2d_pair(sa + Cfg::kABytes + 128 * BK * 2, &tmap_b, leader_full, kb * BK, n0 + 256, kL2EvictNormal);
+          if (w.halves == 2)
+            tma_load_2d_pair(sa + Cfg::kABytes + Cfg::kBHalfBytes, &tmap_b, leader_full, kb * BK, n0 + 256, kL2EvictNormal);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -320,10 +352,10 @@ gemm_tcgen05_2cta_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
   } else if (warp == 1) {
     if (leader && lane == 0) {
       constexpr uint32_t idesc = make_idesc_f16(kBM2, 256);
-      uint32_t stage = 0, phase = 0, it = 0;
+      uint32_t stage = 0, phase = 0;
+      uint32_t uses[2] = {0, 0};  // tiles that have used accumulator h so far
       bool ok = true;
-      for (int t = first_tile; t < num_tiles && ok; t += tile_step, ++it) {
-        const uint32_t tphase = it & 1u;
+      for (int it = 0; ok && wide_tile(p, cluster, nclusters, it, w); ++it) {
         for (int kb = 0; kb < p.kblocks && ok; ++kb) {
           if (!mbar_wait_bounded(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
@@ -331,11 +363,12 @@ gemm_tcgen05_2cta_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
           const uint64_t da = make_sw128_kmajor_desc(sa);
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
+            if (h >= w.halves) break;
             if (kb == 0) {  // the previous tile's epilogue must have drained this half
-              if (!mbar_wait_bounded(&tmem_empty[h], tphase ^ 1u, abort_flag)) { ok = false; break; }
+              if (!mbar_wait_bounded(&tmem_empty[h], (uses[h] & 1u) ^ 1u, abort_flag)) { ok = false; break; }
               tc_fence_after();
             }
-            const uint64_t db = make_sw128_kmajor_desc(sa + Cfg::kABytes + h * 128 * BK * 2);
+            const uint64_t db = make_sw128_kmajor_desc(sa + Cfg::kABytes + h * Cfg::kBHalfBytes);
 #pragma unroll
             for (int k4 = 0; k4 < BK / 16; ++k4)
               umma_f16_pair(tmem_base + h * 256, da + (uint64_t)(k4 * 2), db + (uint64_t)(k4 * 2), idesc,
@@ -345,29 +378,33 @@ gemm_tcgen05_2cta_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
           umma_commit_pair(&empty_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
-        if (ok) { umma_commit_pair(&tmem_full[0]); umma_commit_pair(&tmem_full[1]); }
+        if (ok) {
+          for (int h = 0; h < w.halves; ++h) {
+            umma_commit_pair(&tmem_full[h]);
+            ++uses[h];
+          }
+        }
       }
     }
   } else {
     const int quad = warp & 3;
-    const uint32_t leader_tmem_empty0 = map_to_cta(smem_u32(&tmem_empty[0]), 0);
-    uint32_t it = 0;
-    bool ok = true;
-    for (int t = first_tile; t < num_tiles && ok; t += tile_step, ++it) {
-      const uint32_t tphase = it & 1u;
-      int tm, tn;
-      tile_coords(p, t, tm, tn);
-      const int m0 = tm * kBM2 + (int)cta_rank * 128;
-      const int n0 = p.n_begin + tn * kBNW;
-      for (int h = 0; h < 2; ++h) {
-        if (!mbar_wait_bounded(&tmem_full[h], tphase, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        epilogue_tile<256>(p, tmem_base + h * 256 + ((uint32_t)(quad * 32) << 16),
-                           epi_stage + (warp - 2) * Cfg::kEpiBytesPerWarp, m0 + quad * 32, n0 + h * 256, lane);
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(leader_tmem_empty0 + h * 8u);
-      }
+    const int h = (warp - 2) >> 2;  // the column half this warp drains
+    const uint32_t leader_tmem_empty = map_to_cta(smem_u32(&tmem_empty[h]), 0);
+    uint8_t* stage_tile = epi_stage + (warp - 2) * Cfg::kEpiBytesPerWarp;
+    uint32_t uses = 0;
+    for (int it = 0; wide_tile(p, cluster, nclusters, it, w); ++it) {
+      if (h >= w.halves) continue;
+      const int m0 = w.tm * kBM2 + (int)cta_rank * 128;
+      const int n0 = w.n0 + h * 256;
+      const uint4 bias8 = epilogue_bias8(p, n0, lane);  // in flight while the MMAs finish
+      if (!mbar_wait_bounded(&tmem_full[h], uses & 1u, abort_flag)) break;
+      ++uses;
+      tc_fence_after();
+      epilogue_warp_pipelined<EPI>(p, tmem_base + h * 256 + ((uint32_t)(quad * 32) << 16), stage_tile, bias8,
+                                   m0 + quad * 32, n0, lane);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(leader_tmem_empty);
     }
   }
 
@@ -389,23 +426,50 @@ void choose_tile_order(GemmParams& p, const liger_gemm_args& a, int tile_m, int 
 
 // Launches the 2-CTA kernel.  Returns LIGER_ERR_UNSUPPORTED (without touching the error text) when
 // this shape is better served by the 1-CTA kernel.
-static int launch_gemm_2cta_wide(const liger_gemm_args& a, const GemmParams& p0, int max_clusters, cudaStream_t stream) {
+template <int EPI>
+static int launch_wide_instance(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const GemmParams& p, int clusters,
+                                cudaStream_t stream) {
   using Cfg = Gemm2WideCfg<kStagesWide>;
+  // per launch: the attribute is per device, and a process may drive several
+  LIGER_CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_2cta_wide_kernel<kStagesWide, EPI>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+  gemm_tcgen05_2cta_wide_kernel<kStagesWide, EPI><<<2 * clusters, kWideThreads, Cfg::kSmemBytes, stream>>>(tm_a, tm_b, p);
+  return check_launch("gemm_tcgen05_2cta_wide_kernel");
+}
+
+static int launch_gemm_2cta_wide(const liger_gemm_args& a, const GemmParams& p0, int max_clusters, cudaStream_t stream) {
   GemmParams p = p0;
   p.tiles_m = (a.m + kBM2 - 1) / kBM2;
   p.tiles_n = (a.n_end - a.n_begin + kBNW - 1) / kBNW;
   p.kblocks = (a.k + BK - 1) / BK;
   choose_tile_order(p, a, kBM2, kBNW);
   const int tiles = p.tiles_m * p.tiles_n;
-  LIGER_CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_2cta_wide_kernel<kStagesWide>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      Cfg::kSmemBytes));
+  // last wave: when at most half of the CTA pairs would get a tile, split those tiles into halves
+  p.tail_start = tiles >= max_clusters ? tiles / max_clusters * max_clusters : tiles;
+  p.tail_split = tiles > p.tail_start && 2 * (tiles - p.tail_start) <= max_clusters ? 1 : 0;
   const int clusters = tiles < max_clusters ? tiles : max_clusters;
   CUtensorMap tm_a, tm_b;
   int rc;
   if ((rc = make_tmap_2d_f16(&tm_a, a.a, (uint64_t)a.k, (uint64_t)a.m, (uint64_t)a.lda, BK, 128)) != LIGER_OK) return rc;
   if ((rc = make_tmap_2d_f16(&tm_b, a.wt, (uint64_t)a.k, (uint64_t)a.n, (uint64_t)a.ldw, BK, 128)) != LIGER_OK) return rc;
-  gemm_tcgen05_2cta_wide_kernel<kStagesWide><<<2 * clusters, kGemmThreads, Cfg::kSmemBytes, stream>>>(tm_a, tm_b, p);
-  return check_launch("gemm_tcgen05_2cta_wide_kernel");
+  switch (p.epilogue) {
+    case LIGER_EPI_GELU: return launch_wide_instance<LIGER_EPI_GELU>(tm_a, tm_b, p, clusters, stream);
+    case LIGER_EPI_GEGLU: return launch_wide_instance<LIGER_EPI_GEGLU>(tm_a, tm_b, p, clusters, stream);
+    case LIGER_EPI_QKV_SPLIT: return launch_wide_instance<LIGER_EPI_QKV_SPLIT>(tm_a, tm_b, p, clusters, stream);
+    case LIGER_EPI_RESIDUAL: return launch_wide_instance<LIGER_EPI_RESIDUAL>(tm_a, tm_b, p, clusters, stream);
+    case LIGER_EPI_SCATTER: return launch_wide_instance<LIGER_EPI_SCATTER>(tm_a, tm_b, p, clusters, stream);
+    default: return launch_wide_instance<LIGER_EPI_STORE>(tm_a, tm_b, p, clusters, stream);
+  }
+}
+
+template <int EPI>
+static int launch_pair_instance(const CUtensorMap& tm_a, const CUtensorMap& tm_b, const GemmParams& p, int clusters,
+                                cudaStream_t stream) {
+  using Cfg = Gemm2Cfg<kStages2>;
+  LIGER_CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_2cta_kernel<kStages2, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      Cfg::kSmemBytes));
+  gemm_tcgen05_2cta_kernel<kStages2, EPI><<<2 * clusters, kGemmThreads, Cfg::kSmemBytes, stream>>>(tm_a, tm_b, p);
+  return check_launch("gemm_tcgen05_2cta_kernel");
 }
 
 int launch_gemm_2cta(const liger_gemm_args& a, const GemmParams& p0, int sm_count, cudaStream_t stream) {
@@ -417,9 +481,9 @@ int launch_gemm_2cta(const liger_gemm_args& a, const GemmParams& p0, int sm_coun
   choose_tile_order(p, a, kBM2, kBN2);
   const int tiles = p.tiles_m * p.tiles_n;
   static int max_clusters = -1;
-  LIGER_CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_2cta_kernel<kStages2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      Cfg::kSmemBytes));
   if (max_clusters < 0) {
+    LIGER_CUDA_TRY(cudaFuncSetAttribute(gemm_tcgen05_2cta_kernel<kStages2, LIGER_EPI_STORE>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(sm_count / 2 * 2);
     cfg.blockDim = dim3(kGemmThreads);
@@ -430,7 +494,7 @@ int launch_gemm_2cta(const liger_gemm_args& a, const GemmParams& p0, int sm_coun
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_2cta_kernel<kStages2>, &cfg) != cudaSuccess || n < 1) {
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_tcgen05_2cta_kernel<kStages2, LIGER_EPI_STORE>, &cfg) != cudaSuccess || n < 1) {
       cudaGetLastError();
       n = 0;
     }
@@ -442,9 +506,12 @@ int launch_gemm_2cta(const liger_gemm_args& a, const GemmParams& p0, int sm_coun
     // compare waves x tile width (LIGER_GEMM_WIDE = 0 / 1 forces the choice)
     static int wide_env = -2;
     if (wide_env == -2) { const char* e = getenv("LIGER_GEMM_WIDE"); wide_env = e ? atoi(e) : -1; }
+    // cost in 256x256-tile waves: full wide waves count 2, a split tail (at most half of the CTA pairs busy) 1
     const long tiles_w = (long)p.tiles_m * ((a.n_end - a.n_begin + kBNW - 1) / kBNW);
-    const long waves_w = (tiles_w + max_clusters - 1) / max_clusters, waves_n = ((long)tiles + max_clusters - 1) / max_clusters;
-    const bool geom_ok = a.k >= 8192 && tiles_w >= max_clusters && waves_w * 2 <= waves_n + (waves_n + 9) / 10;
+    const long full_w = tiles_w / max_clusters, rem_w = tiles_w - full_w * max_clusters;
+    const long cost_w = 2 * full_w + (rem_w == 0 ? 0 : 2 * rem_w <= max_clusters ? 1 : 2);
+    const long waves_n = ((long)tiles + max_clusters - 1) / max_clusters;
+    const bool geom_ok = a.k >= 8192 && tiles_w >= max_clusters && cost_w <= waves_n + (waves_n + 9) / 10;
     if (wide_env == 1 || (wide_env < 0 && geom_ok)) return launch_gemm_2cta_wide(a, p0, max_clusters, stream);
   }
   const int clusters = tiles < max_clusters ? tiles : max_clusters;
@@ -452,8 +519,14 @@ int launch_gemm_2cta(const liger_gemm_args& a, const GemmParams& p0, int sm_coun
   int rc;
   if ((rc = make_tmap_2d_f16(&tm_a, a.a, (uint64_t)a.k, (uint64_t)a.m, (uint64_t)a.lda, BK, 128)) != LIGER_OK) return rc;
   if ((rc = make_tmap_2d_f16(&tm_b, a.wt, (uint64_t)a.k, (uint64_t)a.n, (uint64_t)a.ldw, BK, 128)) != LIGER_OK) return rc;
-  gemm_tcgen05_2cta_kernel<kStages2><<<2 * clusters, kGemmThreads, Cfg::kSmemBytes, stream>>>(tm_a, tm_b, p);
-  return check_launch("gemm_tcgen05_2cta_kernel");
+  switch (p.epilogue) {
+    case LIGER_EPI_GELU: return launch_pair_instance<LIGER_EPI_GELU>(tm_a, tm_b, p, clusters, stream);
+    case LIGER_EPI_GEGLU: return launch_pair_instance<LIGER_EPI_GEGLU>(tm_a, tm_b, p, clusters, stream);
+    case LIGER_EPI_QKV_SPLIT: return launch_pair_instance<LIGER_EPI_QKV_SPLIT>(tm_a, tm_b, p, clusters, stream);
+    case LIGER_EPI_RESIDUAL: return launch_pair_instance<LIGER_EPI_RESIDUAL>(tm_a, tm_b, p, clusters, stream);
+    case LIGER_EPI_SCATTER: return launch_pair_instance<LIGER_EPI_SCATTER>(tm_a, tm_b, p, clusters, stream);
+    default: return launch_pair_instance<LIGER_EPI_STORE>(tm_a, tm_b, p, clusters, stream);
+  }
 }
 
 int gemm_2cta_max_clusters_hint(int sm_count) { return sm_count / 2; }

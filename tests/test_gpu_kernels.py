@@ -188,6 +188,51 @@ def test_gemm_linearity_at_full_size(gpu, liger):
         assert abs(y1[r, c].item() - want) <= 1e-2 * max(1.0, abs(want))
 
 
+@pytest.mark.parametrize("epi", ["store", "residual", "qkv", "geglu", "gelu"])
+@pytest.mark.parametrize("n_end", [12288, 12224])
+def test_gemm_long_k_whole_equals_slices_bitwise(gpu, liger, epi, n_end):
+    """At long K the whole launch runs on 256x512 tiles (with a split last wave at this shape, and a
+    partial last tile for n_end = 12224) while the eight slices are too small for them and take the
+    256x256 kernel: every epilogue must give the same bits either way, and sampled entries must match
+    an fp64 dot product."""
+    import torch
+    m, n, k, factor = 4096, 12288, 8192, 8
+    B, S, h, D = 8, 512, 32, 128
+    a = dev_fill(liger, m, k, 0, 300, std=0.5)
+    wt = dev_fill(liger, k, n, 0, 301, std=0.02, mode=1)
+    bias = dev_fill(liger, 1, n, 0, 302, std=0.02).reshape(-1)
+    res = dev_fill(liger, m, n, 0, 303) if epi == "residual" else None
+    code = {"store": 0, "gelu": liger.capi.EPI_GELU, "geglu": liger.capi.EPI_GEGLU, "qkv": liger.capi.EPI_QKV_SPLIT,
+            "residual": liger.capi.EPI_RESIDUAL}[epi]
+
+    def run(slices):
+        kw = dict(epi=code, bias=bias, residual=res)
+        if epi == "qkv":
+            qkv = [torch.zeros((B, h, S, D), dtype=torch.float16, device="cuda") for _ in range(3)]
+            kw.update(qkv=qkv, seq_len=S, heads=h, head_dim=D)
+        else:
+            kw.update(out=torch.zeros((m, n // 2 if epi == "geglu" else n), dtype=torch.float16, device="cuda"))
+        for lo, hi in slices:
+            if lo < hi:
+                gemm(liger, a, wt, n_begin=lo, n_end=hi, **kw)
+        return kw["qkv"] if epi == "qkv" else [kw["out"]]
+
+    whole = run([(0, n_end)])
+    step = n // factor
+    parts = run([(i * step, min((i + 1) * step, n_end)) for i in range(factor)])
+    check_status(liger)
+    for w_, p_ in zip(whole, parts):
+        assert torch.equal(w_, p_)
+    if epi == "store":
+        g = torch.Generator().manual_seed(1)
+        rows = torch.randint(0, m, (64,), generator=g).tolist()
+        cols = torch.randint(0, n_end, (64,), generator=g).tolist()
+        for r, c in zip(rows, cols):
+            want = (a[r].double() * wt[c].double()).sum().item() + bias[c].item()
+            assert abs(whole[0][r, c].item() - want) <= 1e-2 * max(1.0, abs(want))
+        assert whole[0][:, n_end:].abs().max().item() == 0 if n_end < n else True
+
+
 # ---------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("m,n", [(7, 1024), (512, 12288), (3, 8), (5, 16384)])
 def test_layernorm(gpu, liger, oracle, m, n):
