@@ -131,6 +131,11 @@ def cpu_port_tokens_per_s():
 REF_HARNESS = os.path.join(ROOT, "oracle", "_ref", "liger_ref_harness")
 
 
+# DRAM bytes per GEMM launch at N=1 (read + write, average of the QKV / out-proj / FFN-up / FFN-down launches of
+# one layer), from the one-pass ncu capture summarised under profiles/.
+GEMM_DRAM_BYTES_PER_LAUNCH_TP1 = 4.44e9
+
+
 def run_reference_gpu_build(args, rank, world):
     """The reference's own NCCL + cuBLAS build (unmodified sources + oracle/ref_harness/harness.cu, compiled
     for sm_100a into oracle/_ref/), one process per GPU over the MPI stand-in.  The reference can only
@@ -359,10 +364,14 @@ def main():
                     "api": "liger_model_forward_host: pinned host buffers, copies on the launch stream, host sync per step; "
                            "with N > 1 each rank uploads 1/N of the input rows (gathered over NVLink) and rank 0 downloads the result"},
             "gpu_launches": launches,
-            "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_kernel (QKV, out-proj, FFN-up, FFN-down launches)",
+            "roofline": {"bound": "tensor", "kernel": "gemm_tcgen05_2cta_wide_kernel / gemm_tcgen05_2cta_kernel (QKV, out-proj, FFN-up, FFN-down launches)",
                          "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
                          "peak_source": peaks["source"], "frac_of_nominal_2250": achieved / 2250.0,
-                         "traffic": None, "launches_timed": gemm_launches,
+                         "traffic": GEMM_DRAM_BYTES_PER_LAUNCH_TP1 if world == 1 else None,
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, average over the four GEMM "
+                                           "launches of a layer at N=1 (profiles/gemm_tcgen05_2cta_wide_glm130b_tp1.md); "
+                                           "not captured for N>1",
+                         "launches_timed": gemm_launches,
                          "share_of_step": gemm_ms / total_k_ms if total_k_ms else None},
             "kernels": per_kernel,
             "allreduce_split": comm_split,
