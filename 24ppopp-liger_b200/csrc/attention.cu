@@ -8,6 +8,7 @@
 //
 // Decode: one query token per sequence against a KV cache, split over the KV length so that the
 // cache streams at HBM rate; a second kernel merges the split partials.
+#include <cstdlib>
 #include <mutex>
 
 #include "runtime.h"
@@ -339,6 +340,15 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ scratch,
   out[(size_t)b * ldo + head * D + d] = __float2half_rn(a / (ll + 1e-6f));
 }
 
+// attention_sm100.cu: the tcgen05 kernel (head_dim 128, no mask tensor)
+int launch_attention_prefill_tc(const void* q, const void* k, const void* v, void* out, int batch, int heads, int seq_len,
+                                int ldo, float scale, int causal, cudaStream_t stream);
+static bool tc_attention_enabled() {
+  static int on = -1;  // LIGER_ATTN_TC=0 keeps every shape on the mma.sync kernel
+  if (on < 0) { const char* e = getenv("LIGER_ATTN_TC"); on = (e && atoi(e) == 0) ? 0 : 1; }
+  return on != 0;
+}
+
 template <int D>
 static int launch_prefill(const void* q, const void* k, const void* v, const void* mask, void* out, int batch, int heads,
                           int S, int ldo, float scale, int causal, cudaStream_t stream) {
@@ -366,6 +376,10 @@ extern "C" int liger_attention_prefill(const void* q, const void* k, const void*
   if (batch > 65535 || heads > 65535) return set_error(LIGER_ERR_UNSUPPORTED, "attention_prefill: batch, heads <= 65535");
   if (!current_device()) return LIGER_ERR_CUDA;
   cudaStream_t s = (cudaStream_t)stream;
+  if (head_dim == 128 && mask == nullptr && seq_len >= 128 && tc_attention_enabled()) {
+    const int rc = launch_attention_prefill_tc(q, k, v, out, batch, heads, seq_len, ldo, scale, causal, s);
+    if (rc != LIGER_ERR_UNSUPPORTED) return rc;
+  }
   if (head_dim == 64) return launch_prefill<64>(q, k, v, mask, out, batch, heads, seq_len, ldo, scale, causal, s);
   if (head_dim == 128) return launch_prefill<128>(q, k, v, mask, out, batch, heads, seq_len, ldo, scale, causal, s);
   return set_error(LIGER_ERR_UNSUPPORTED, "attention_prefill: head_dim %d (64 and 128 are implemented)", head_dim);

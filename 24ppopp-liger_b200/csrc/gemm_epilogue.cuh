@@ -247,18 +247,6 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
 // before the accumulator is ready) and handed round by shuffles; destination addresses are split into a per-lane column part computed once
 // per pass and a row part advanced without divisions.
 
-// tcgen05.wait::ld that also names the loaded registers, so that no use of them can be scheduled
-// ahead of the wait.
-__device__ __forceinline__ void tmem_ld_wait_regs(uint32_t (&r)[32]) {
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
-                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
-                 "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
-                 "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
-               :
-               : "memory");
-}
-
 // Staged [32 x 64] output tile -> global memory; a warp instruction stores 4 rows of 128 contiguous bytes.
 template <int EPI>
 __device__ __forceinline__ void stage_writeout64(const GemmParams& p, uint8_t* stage, int row0, int out_col0, int out_end,

@@ -109,6 +109,27 @@ int make_tmap_2d_f16(CUtensorMap* map, const void* base, uint64_t inner, uint64_
   return LIGER_OK;
 }
 
+int make_tmap_3d_f16(CUtensorMap* map, const void* base, uint64_t inner, uint64_t n1, uint64_t n2, uint32_t box_inner,
+                     uint32_t box_n1) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return set_error(LIGER_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  if (((uintptr_t)base & 15u) != 0 || (inner * 2) % 16 != 0)
+    return set_error(LIGER_ERR_INVALID, "tensor map: base %p / row %llu B must be 16-byte aligned", base,
+                     (unsigned long long)(inner * 2));
+  cuuint64_t dims[3] = {inner, n1, n2};
+  cuuint64_t strides[2] = {inner * 2, inner * n1 * 2};
+  cuuint32_t box[3] = {box_inner, box_n1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUtensorMapSwizzle sw = (box_inner * 2 == 128) ? CU_TENSOR_MAP_SWIZZLE_128B
+                          : (box_inner * 2 == 64) ? CU_TENSOR_MAP_SWIZZLE_64B
+                                                  : CU_TENSOR_MAP_SWIZZLE_NONE;
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return set_error(LIGER_ERR_CUDA, "cuTensorMapEncodeTiled (3-D) failed with CUresult %d", (int)r);
+  return LIGER_OK;
+}
+
 int check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(LIGER_ERR_CUDA, "%s launch failed: %s", what, cudaGetErrorString(e));

@@ -38,6 +38,10 @@ int require_sm100(const DeviceInfo** out);
 int make_tmap_2d_f16(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t ld,
                      uint32_t box_inner, uint32_t box_outer);
 
+// 3-D fp16 tensor map over a contiguous [n2][n1][inner] array; box = box_inner x box_n1 x 1.
+int make_tmap_3d_f16(CUtensorMap* map, const void* base, uint64_t inner, uint64_t n1, uint64_t n2, uint32_t box_inner,
+                     uint32_t box_n1);
+
 // Launch-error check after a <<<>>> launch.
 int check_launch(const char* what);
 
