@@ -36,7 +36,8 @@ constexpr int kTcThreads = 576;  // 18 warps
 constexpr int kBoxBytes = 128 * 64 * 2;   // one swizzled box: 128 rows x 64 fp16
 constexpr int kTileBytes = 2 * kBoxBytes; // a [128 x 128] fp16 tile = two boxes (columns 0-63, 64-127)
 constexpr int kExchBytes = (2 * 4 + 2 * 4) * 128 * 4;  // row maxima [2 stages][4 column groups][128 rows], row sums [2 items][4][128]
-constexpr int kTcSmemBytes = 6 * kTileBytes /* Q, K x2, V x2, P */ + kExchBytes + 512 + 1024;
+constexpr int kOutScratchBytes = 16 * 512;  // per softmax warp: 8 rows x 64 B of output being regrouped for coalesced stores
+constexpr int kTcSmemBytes = 6 * kTileBytes /* Q, K x2, V x2, P */ + kExchBytes + kOutScratchBytes + 512 + 1024;
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct AttnTcParams {
@@ -123,7 +124,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
   uint8_t* sP = sV + 2 * kTileBytes;
   float* xmax = reinterpret_cast<float*>(sP + kTileBytes);  // [2][4][128]
   float* lsum = xmax + 2 * 4 * 128;                         // [2][4][128]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(lsum + 2 * 4 * 128);
+  uint8_t* out_scratch = reinterpret_cast<uint8_t*>(lsum + 2 * 4 * 128);  // [16 warps][512 B]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(out_scratch + kOutScratchBytes);
   uint64_t* q_full = bars;        // [1]
   uint64_t* q_empty = bars + 1;   // [1]
   uint64_t* k_full = bars + 2;    // [2]
@@ -268,19 +270,33 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __
       uint32_t t[32];
       tmem_ld_32x32(tmem_base + 256 + ob * 128 + cg * 32 + lane_sel, t);
       tmem_ld_wait_regs(t);
-      if (q.qi < p.S) {
-        const float inv = 1.0f / (l_tot + 1e-6f);
-        const int b = q.bh / p.heads, head = q.bh - b * p.heads;
-        __half* dst = p.out + ((size_t)b * p.S + q.qi) * p.ldo + (size_t)head * 128 + cg * 32;
+      // thread = row holds 64 contiguous output bytes; a warp store of one 16-byte piece per row would touch
+      // 32 different lines.  Regroup 8 rows at a time through 512 B of shared memory so that every store
+      // instruction writes 8 rows x 64 contiguous bytes.
+      const float inv = 1.0f / (l_tot + 1e-6f);
+      uint4 u[4];
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          uint4 u;
-          u.x = pack_half2(__uint_as_float(t[q4 * 8 + 0]) * inv, __uint_as_float(t[q4 * 8 + 1]) * inv);
-          u.y = pack_half2(__uint_as_float(t[q4 * 8 + 2]) * inv, __uint_as_float(t[q4 * 8 + 3]) * inv);
-          u.z = pack_half2(__uint_as_float(t[q4 * 8 + 4]) * inv, __uint_as_float(t[q4 * 8 + 5]) * inv);
-          u.w = pack_half2(__uint_as_float(t[q4 * 8 + 6]) * inv, __uint_as_float(t[q4 * 8 + 7]) * inv);
-          *reinterpret_cast<uint4*>(dst + q4 * 8) = u;
+      for (int q4 = 0; q4 < 4; ++q4) {
+        u[q4].x = pack_half2(__uint_as_float(t[q4 * 8 + 0]) * inv, __uint_as_float(t[q4 * 8 + 1]) * inv);
+        u[q4].y = pack_half2(__uint_as_float(t[q4 * 8 + 2]) * inv, __uint_as_float(t[q4 * 8 + 3]) * inv);
+        u[q4].z = pack_half2(__uint_as_float(t[q4 * 8 + 4]) * inv, __uint_as_float(t[q4 * 8 + 5]) * inv);
+        u[q4].w = pack_half2(__uint_as_float(t[q4 * 8 + 6]) * inv, __uint_as_float(t[q4 * 8 + 7]) * inv);
+      }
+      uint8_t* scr = out_scratch + (warp - 2) * 512;
+      const int b = q.bh / p.heads, head = q.bh - b * p.heads;
+      const int q_row0 = q.qi - lane;  // first row of this warp's 32
+      __half* obase = p.out + (size_t)b * p.S * p.ldo + (size_t)head * 128 + cg * 32 + (lane & 3) * 8;
+#pragma unroll
+      for (int pass = 0; pass < 4; ++pass) {
+        if ((lane >> 3) == pass) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) *reinterpret_cast<uint4*>(scr + (lane & 7) * 64 + q4 * 16) = u[q4];
         }
+        __syncwarp();
+        const uint4 piece = *reinterpret_cast<const uint4*>(scr + lane * 16);
+        const int row = q_row0 + pass * 8 + (lane >> 2);
+        if (row < p.S) *reinterpret_cast<uint4*>(obase + (size_t)row * p.ldo) = piece;
+        __syncwarp();
       }
       tc_fence_before();
       __syncwarp();

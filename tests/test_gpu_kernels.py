@@ -309,7 +309,12 @@ def test_transpose_weight(gpu, liger):
 # ---------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("B,h,S,D,mode", [(2, 3, 128, 64, "causal"), (1, 2, 100, 128, "causal"), (2, 2, 64, 64, "none"),
                                           (1, 2, 130, 64, "mask"), (2, 4, 512, 128, "causal"), (1, 1, 2, 64, "mask"),
-                                          (1, 2, 320, 128, "mask")])
+                                          (1, 2, 320, 128, "mask"),
+                                          # head_dim 128 without a mask tensor, seq >= 128: the tcgen05 kernel (ragged last
+                                          # key block / query tile, one and several key blocks, more items than SMs)
+                                          (2, 3, 256, 128, "causal"), (1, 2, 200, 128, "causal"), (1, 4, 384, 128, "none"),
+                                          (2, 2, 130, 128, "causal"), (1, 3, 128, 128, "none"), (3, 64, 512, 128, "causal"),
+                                          (1, 2, 1100, 128, "causal")])
 def test_attention_prefill(gpu, liger, oracle, B, h, S, D, mode):
     import torch
     q = dev_fill(liger, B * h * S, D, 0, 400).reshape(B, h, S, D)
@@ -329,6 +334,7 @@ def test_attention_prefill(gpu, liger, oracle, B, h, S, D, mode):
     want = oracle.merge_heads(oracle.attention(to_np(q), to_np(k), to_np(v), mask=mask_np, causal=(mode == "causal"),
                                                scale=scale))
     assert_close(to_np(out), want, rel=1e-2, what=f"attention {mode}")
+    check_status(liger)
 
 
 @pytest.mark.parametrize("B,h,L,D", [(2, 3, 300, 128), (4, 2, 2048, 128), (1, 2, 17, 64), (3, 1, 256, 64)])
