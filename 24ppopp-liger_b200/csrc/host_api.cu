@@ -30,6 +30,8 @@ struct liger_model {
   size_t ev_chain_next = 0;
   std::vector<cudaEvent_t> ev_pool;                      // reusable events
   std::vector<std::pair<int, std::pair<cudaEvent_t, cudaEvent_t>>> ev_rec;  // (name, (before, after))
+  cudaStream_t copy_in = nullptr, copy_out = nullptr;  // host-buffer entry point: copies overlapped with the first / last kernels
+  cudaEvent_t ev_io[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
   bool timeline = false;  // record per-kernel events in interleaved passes too (diagnostics)
   struct TimelineRec { int name, stream; cudaEvent_t e0, e1; };
   std::vector<TimelineRec> tl_rec;
@@ -313,6 +315,85 @@ extern "C" int liger_model_set_micro_batches(liger_model* m, int micro_batches) 
   return LIGER_OK;
 }
 
+// world_size == 1, even batch: the two halves of the batch are uploaded one after the other and the
+// first kernels (input LayerNorm, QKV GEMM) run per half, so that the second upload hides behind the
+// first half's GEMM; likewise the last GEMM runs per half and the first half's download hides behind
+// the second half's GEMM.  Rows are independent in those kernels, so the result is bit for bit the
+// one of the un-split launch.  Returns the number of launches, or 0 if this form does not apply.
+static int forward_host_pipelined(liger_model* m, const void* host_input, void* host_output, int batch, int seq_len, int slot,
+                                  cudaStream_t s) {
+  Bert_Model& b = *m->model;
+  if (m->timing || (batch & 1) || m->sp.world_size != 1) return 0;
+  std::vector<FuncWrap> vec = b.forward(m->io_in, m->io_out, batch, seq_len, slot);
+  const bool ln_first = vec.size() >= 2 && vec[0].name == kPrologueName && vec[1].type == GEMM && vec[1].name == 0;
+  const size_t first_gemm = ln_first ? 1 : 0;
+  if (vec.size() < 4 || vec[first_gemm].type != GEMM || vec[first_gemm].name != 0 || vec.back().type != GEMM) return 0;
+  const GEMM_ARGS g0 = vec[first_gemm].args_gemm_tuple, gl = vec.back().args_gemm_tuple;
+  if (g0.epilogue != LIGER_EPI_QKV_SPLIT || g0.kv_stride != 0 || g0.a != (const void*)(ln_first ? b.slots[slot].normed : m->io_in) ||
+      gl.c != (void*)m->io_out || (gl.epilogue != LIGER_EPI_STORE && gl.epilogue != LIGER_EPI_RESIDUAL))
+    return 0;
+  if (!m->copy_in) {
+    LIGER_CUDA_TRY(cudaStreamCreateWithFlags(&m->copy_in, cudaStreamNonBlocking));
+    LIGER_CUDA_TRY(cudaStreamCreateWithFlags(&m->copy_out, cudaStreamNonBlocking));
+    for (auto& e : m->ev_io) LIGER_CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  }
+  const int hb = batch / 2, rows = hb * seq_len, H = b.H;
+  const size_t half_bytes = (size_t)rows * H * 2;
+  const char* hin = (const char*)host_input;
+  char* hout = (char*)host_output;
+  // uploads: ordered after everything the caller has queued (the previous step may still read io_in)
+  LIGER_CUDA_TRY(cudaEventRecord(m->ev_io[0], s));
+  LIGER_CUDA_TRY(cudaStreamWaitEvent(m->copy_in, m->ev_io[0], 0));
+  LIGER_CUDA_TRY(cudaMemcpyAsync(m->io_in, hin, half_bytes, cudaMemcpyHostToDevice, m->copy_in));
+  LIGER_CUDA_TRY(cudaEventRecord(m->ev_io[1], m->copy_in));
+  LIGER_CUDA_TRY(cudaMemcpyAsync((char*)m->io_in + half_bytes, hin + half_bytes, half_bytes, cudaMemcpyHostToDevice, m->copy_in));
+  LIGER_CUDA_TRY(cudaEventRecord(m->ev_io[2], m->copy_in));
+  int n = 0, rc;
+  for (int h = 0; h < 2; ++h) {
+    LIGER_CUDA_TRY(cudaStreamWaitEvent(s, m->ev_io[1 + h], 0));
+    if (ln_first) {
+      const LayerNorm* ln = b.encoders[0]->ln_mha;
+      rc = liger_layernorm(m->io_in + (size_t)h * rows * H, ln->gamma, ln->beta, b.slots[slot].normed + (size_t)h * rows * H, rows,
+                           H, s);
+      if (rc != LIGER_OK) return rc;
+      ++n;
+    }
+    GEMM_ARGS a = g0;
+    a.m = rows;
+    a.a = (const half_t*)g0.a + (size_t)h * rows * g0.lda;
+    const size_t head_off = (size_t)h * hb * g0.heads * seq_len * g0.head_dim;  // [B, h, S, D]: the batch is the outer dimension
+    a.q_out = (half_t*)g0.q_out + head_off;
+    a.k_out = (half_t*)g0.k_out + head_off;
+    a.v_out = (half_t*)g0.v_out + head_off;
+    if ((rc = liger_gemm_fp16(&a, s)) != LIGER_OK) return rc;
+    ++n;
+  }
+  DynamicNvInitParam dp;
+  dp.stream = s;
+  for (size_t i = first_gemm + 1; i + 1 < vec.size(); ++i) {
+    if ((rc = vec[i].callback(dp)) != LIGER_OK) return rc;
+    ++n;
+  }
+  for (int h = 0; h < 2; ++h) {
+    GEMM_ARGS a = gl;
+    a.m = rows;
+    a.a = (const half_t*)gl.a + (size_t)h * rows * gl.lda;
+    a.c = (half_t*)gl.c + (size_t)h * rows * gl.ldc;
+    if (gl.residual) a.residual = (const half_t*)gl.residual + (size_t)h * rows * gl.ldr;
+    if ((rc = liger_gemm_fp16(&a, s)) != LIGER_OK) return rc;
+    ++n;
+    if (h == 0) {
+      LIGER_CUDA_TRY(cudaEventRecord(m->ev_io[3], s));
+      LIGER_CUDA_TRY(cudaStreamWaitEvent(m->copy_out, m->ev_io[3], 0));
+      LIGER_CUDA_TRY(cudaMemcpyAsync(hout, m->io_out, half_bytes, cudaMemcpyDeviceToHost, m->copy_out));
+      LIGER_CUDA_TRY(cudaEventRecord(m->ev_io[4], m->copy_out));
+    }
+  }
+  LIGER_CUDA_TRY(cudaMemcpyAsync(hout + half_bytes, (char*)m->io_out + half_bytes, half_bytes, cudaMemcpyDeviceToHost, s));
+  LIGER_CUDA_TRY(cudaStreamWaitEvent(s, m->ev_io[4], 0));  // the caller's stream covers the first half's download too
+  return n;
+}
+
 extern "C" int liger_model_forward_host(liger_model* m, const void* host_input, void* host_output, int batch, int seq_len,
                                         int slot, void* stream) {
   if (!m || !host_input || !host_output) return liger::set_error(LIGER_ERR_INVALID, "model_forward_host: null argument");
@@ -325,6 +406,12 @@ extern "C" int liger_model_forward_host(liger_model* m, const void* host_input, 
   if (slot < 0) { slot = b.next_slot; b.next_slot = (b.next_slot + 1) % (int)b.slots.size(); }
   if (slot >= (int)b.slots.size()) return liger::set_error(LIGER_ERR_INVALID, "model_forward_host: slot %d", slot);
   if (ws == 1) {
+    try {
+      const int np = forward_host_pipelined(m, host_input, host_output, batch, seq_len, slot, s);
+      if (np != 0) return np;
+    } catch (const std::exception& e) {
+      return liger::set_error(LIGER_ERR_INVALID, "model_forward_host: %s", e.what());
+    }
     LIGER_CUDA_TRY(cudaMemcpyAsync(m->io_in, host_input, bytes, cudaMemcpyHostToDevice, s));
     const int n = liger_model_forward(m, m->io_in, m->io_out, batch, seq_len, slot, stream);
     if (n < 0) return n;
