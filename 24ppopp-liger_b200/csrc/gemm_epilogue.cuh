@@ -404,31 +404,53 @@ __device__ __forceinline__ void epilogue_warp_pipelined(const GemmParams& p, uin
     }
   } else {
     const int nu = min(8, (p.n_end - n0 + 31) / 32);
-    const __half* res_row = nullptr;
-    if constexpr (EPI == LIGER_EPI_RESIDUAL) res_row = p.residual + (size_t)(row < p.m ? row : 0) * p.ldr + n0;
     uint32_t r0[32], r1[32];
-    uint4 q0[4] = {}, q1[4] = {};
-    auto fetch = [&](int u, uint32_t (&r)[32], uint4 (&q)[4]) {
-      tmem_ld_32x32(taddr + u * 32, r);
+    uint4 q[4] = {};
+    // RESIDUAL: the residual tile of a pass (32 rows x 64 columns) is read with row-contiguous loads (4 rows x
+    // 128 B per instruction, the write-out mapping) one pass ahead, parked in registers, and dropped into the
+    // staging tile before the pass's math, which picks its row's values up from there.  Row-per-thread
+    // loads would touch 32 lines per instruction and cost more than the rest of the epilogue together.
+    uint4 rs[8];
+    const int wch = lane & 7, wrsub = lane >> 3;
+    auto load_residual = [&](int u) {  // pass starting at unit u
       if constexpr (EPI == LIGER_EPI_RESIDUAL) {
+        const int col = n0 + u * 32 + wch * 8;
 #pragma unroll
-        for (int g = 0; g < 4; ++g)
-          if (n0 + u * 32 + g * 8 < p.n_end) q[g] = __ldg(reinterpret_cast<const uint4*>(res_row + u * 32 + g * 8));
+        for (int i = 0; i < 8; ++i) {
+          const int rr = row0 + wrsub + i * 4;
+          rs[i] = (rr < p.m && col < p.n_end) ? __ldg(reinterpret_cast<const uint4*>(p.residual + (size_t)rr * p.ldr + col))
+                                              : make_uint4(0u, 0u, 0u, 0u);
+        }
       }
     };
-    fetch(0, r0, q0);
+    load_residual(0);
+    tmem_ld_32x32(taddr, r0);
 #pragma unroll 1
     for (int u = 0; u < nu; u += 2) {
       uint4 o[4];
+      if constexpr (EPI == LIGER_EPI_RESIDUAL) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) *stage_slot<64>(stage, wrsub + i * 4, wch) = rs[i];
+        __syncwarp();
+        if (u + 2 < nu) load_residual(u + 2);
+      }
       tmem_ld_wait_regs(r0);
-      if (u + 1 < nu) fetch(u + 1, r1, q1);
-      unit_math<EPI>(bias8, u * 32, r0, q0, o);
+      if (u + 1 < nu) tmem_ld_32x32(taddr + (u + 1) * 32, r1);
+      if constexpr (EPI == LIGER_EPI_RESIDUAL) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) q[j] = *stage_slot<64>(stage, lane, j);
+      }
+      unit_math<EPI>(bias8, u * 32, r0, q, o);
 #pragma unroll
       for (int j = 0; j < 4; ++j) *stage_slot<64>(stage, lane, j) = o[j];
       if (u + 1 < nu) {
         tmem_ld_wait_regs(r1);
-        if (u + 2 < nu) fetch(u + 2, r0, q0);
-        unit_math<EPI>(bias8, (u + 1) * 32, r1, q1, o);
+        if (u + 2 < nu) tmem_ld_32x32(taddr + (u + 2) * 32, r0);
+        if constexpr (EPI == LIGER_EPI_RESIDUAL) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) q[j] = *stage_slot<64>(stage, lane, 4 + j);
+        }
+        unit_math<EPI>(bias8, (u + 1) * 32, r1, q, o);
 #pragma unroll
         for (int j = 0; j < 4; ++j) *stage_slot<64>(stage, lane, 4 + j) = o[j];
       }
