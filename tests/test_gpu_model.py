@@ -27,6 +27,10 @@ CASES = {
     "preln_two_shot": dict(head_num=16, size_per_head=64, layer_num=2, graph=1, act=0, ffn_inner=2048, causal=1, B=4, S=264),
     "ref_two_shot": dict(head_num=16, size_per_head=64, layer_num=1, graph=0, act=1, ffn_inner=2048, causal=0, B=2, S=520),
     "ref_geglu_causal": dict(head_num=8, size_per_head=64, layer_num=1, graph=0, act=1, ffn_inner=2048, causal=1, B=1, S=200),
+    # big enough for the CTA-pair GEMM kernels (256x256 and, in the FFN-down GEMM with K >= 8192, 256x512 tiles) with
+    # every epilogue kind including the scatter to the owning rank at TP = 2, and for the tcgen05 attention kernel
+    "preln_pair_kernels": dict(head_num=32, size_per_head=128, layer_num=1, graph=1, act=0, ffn_inner=16384, causal=1, B=8,
+                               S=512),
 }
 
 
@@ -150,7 +154,8 @@ def _tp_worker(rank, world, port, case, results):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("case", ["tiny_preln", "ref_gelu", "preln_geglu", "preln_two_shot", "ref_two_shot"])
+@pytest.mark.parametrize("case", ["tiny_preln", "ref_gelu", "preln_geglu", "preln_two_shot", "ref_two_shot",
+                                  "preln_pair_kernels"])
 def test_stack_forward_tensor_parallel_2(oracle, case):
     """BASELINE config 1 is the tiny pre-LN stack at TP = 2."""
     import torch
