@@ -207,6 +207,8 @@ def main():
     ap.add_argument("--impl", default="liger", choices=["liger", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--layers", type=int, default=WORKLOAD["layers"], help=argparse.SUPPRESS)
+    ap.add_argument("--micro-batches", type=int, default=0,
+                    help="batch halves interleaved on two streams (0 = default: 2 with more than one GPU)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -244,7 +246,8 @@ def main():
         comm = Comm(rank, world, lib.liger_model_comm_bytes(C.byref(cfg), world), channels=4)
     model = C.c_void_p()
     liger.check(lib.liger_model_create(C.byref(model), C.byref(cfg), rank, world, comm.handle if comm else None))
-    micro = 2 if world > 1 else 1   # halves of the batch interleaved on two streams (hides the all-reduces)
+    # halves of the batch interleaved on two streams (hides the all-reduces)
+    micro = args.micro_batches if args.micro_batches > 0 else (2 if world > 1 else 1)
     liger.check(lib.liger_model_set_micro_batches(model, micro))
 
     stream = torch.cuda.current_stream()
