@@ -243,8 +243,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tadd
 // ---- pipelined epilogue ------------------------------------------------------------------------------
 // Used where the epilogue is not hidden behind the next tile's MMAs (the 256x512 kernel, whose tile
 // owns all of TMEM).  Differences from epilogue_tile: the TMEM load (and the residual load) of unit
-// u+1 is in flight while unit u is converted; the bias is read once per tile (8 columns per lane,
-// before the accumulator is ready) and handed round by shuffles; destination addresses are split into a per-lane column part computed once
+// u+1 is in flight while unit u is converted; the bias lines are prefetched into L1 before the accumulator
+// is ready and read with broadcast loads; destination addresses are split into a per-lane column part computed once
 // per pass and a row part advanced without divisions.
 
 // Staged [32 x 64] output tile -> global memory; a warp instruction stores 4 rows of 128 contiguous bytes.
@@ -298,20 +298,22 @@ __device__ __forceinline__ void stage_writeout64(const GemmParams& p, uint8_t* s
   }
 }
 
-// Lane j of the warp holds the bias of columns [8j, 8j+8) of the warp's 256-column range.
-__device__ __forceinline__ uint4 bias_group(const uint4& bias8, int group) {
-  uint4 b;
-  b.x = __shfl_sync(0xffffffffu, bias8.x, group);
-  b.y = __shfl_sync(0xffffffffu, bias8.y, group);
-  b.z = __shfl_sync(0xffffffffu, bias8.z, group);
-  b.w = __shfl_sync(0xffffffffu, bias8.w, group);
-  return b;
+// Bias of the warp's 256-column range: `ptr` points at its first column, groups (of 8 columns) at or past
+// `groups` do not exist (past n_end, or no bias vector at all).  Every lane needs the same values, so a
+// group is one broadcast 16-byte load; the lines are in L1 after epilogue_bias8's prefetch.  (Handing the
+// values round with shuffles instead costs 16 shuffles per 32 columns and was a quarter of the epilogue.)
+struct BiasRef {
+  const __half* ptr;
+  int groups;
+};
+__device__ __forceinline__ uint4 bias_group(const BiasRef& b, int group) {
+  return group < b.groups ? __ldg(reinterpret_cast<const uint4*>(b.ptr) + group) : make_uint4(0u, 0u, 0u, 0u);
 }
 
 // 32 accumulator columns of one row (columns [cl, cl+32) of the warp's range) + bias [+ residual /
 // GELU] -> 32 fp16 values
 template <int EPI>
-__device__ __forceinline__ void unit_math(const uint4& bias8, int cl, const uint32_t (&r)[32], const uint4 (&res)[4],
+__device__ __forceinline__ void unit_math(const BiasRef& bias8, int cl, const uint32_t (&r)[32], const uint4 (&res)[4],
                                           uint4 (&o)[4]) {
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
@@ -334,7 +336,7 @@ __device__ __forceinline__ void unit_math(const uint4& bias8, int cl, const uint
   }
 }
 
-__device__ __forceinline__ void unit_math_geglu(const uint4& bias8, int cl, const uint32_t (&gt)[32],
+__device__ __forceinline__ void unit_math_geglu(const BiasRef& bias8, int cl, const uint32_t (&gt)[32],
                                                 const uint32_t (&up)[32], uint4 (&o)[4]) {
 #pragma unroll
   for (int q = 0; q < 4; ++q) {
@@ -354,19 +356,22 @@ __device__ __forceinline__ void unit_math_geglu(const uint4& bias8, int cl, cons
   }
 }
 
-// Bias of columns [n0 + 8*lane, +8) (zeros past n_end or without a bias vector).
-__device__ __forceinline__ uint4 epilogue_bias8(const GemmParams& p, int n0, int lane) {
-  const int col = n0 + lane * 8;
-  if (p.bias == nullptr || col >= p.n_end) return make_uint4(0u, 0u, 0u, 0u);
-  return __ldg(reinterpret_cast<const uint4*>(p.bias + col));
+// Called before the accumulator is ready: touches the warp's bias lines (one 16-byte piece per lane) so that
+// the broadcast loads of the epilogue proper hit in L1, and returns the reference the epilogue uses.
+__device__ __forceinline__ BiasRef epilogue_bias8(const GemmParams& p, int n0, int lane) {
+  BiasRef b;
+  b.ptr = p.bias != nullptr ? p.bias + n0 : nullptr;
+  b.groups = (p.bias != nullptr && n0 < p.n_end) ? min(32, (p.n_end - n0 + 7) >> 3) : 0;
+  if (lane < b.groups) asm volatile("prefetch.global.L1 [%0];" ::"l"(b.ptr + lane * 8));
+  return b;
 }
 
 // One warp's share of an accumulator: TMEM lanes [taddr.lane, +32) x 256 columns starting at
 // accumulator column n0 -> rows [row0, row0+32).  `stage` is the warp's [32 x 64] staging tile,
-// `bias8` this lane's 8 bias values (see epilogue_bias8).
+// `bias8` the warp's bias reference (see epilogue_bias8).
 template <int EPI>
 __device__ __forceinline__ void epilogue_warp_pipelined(const GemmParams& p, uint32_t taddr, uint8_t* stage,
-                                                        const uint4& bias8, int row0, int n0, int lane) {
+                                                        const BiasRef& bias8, int row0, int n0, int lane) {
   if (n0 >= p.n_end) return;
   const int row = row0 + lane;
   if constexpr (EPI == LIGER_EPI_GEGLU) {

@@ -207,7 +207,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       tile_coords(p, t, tm, tn);
       const int m0 = tm * kBM2 + (int)cta_rank * 128;
       const int n0 = p.n_begin + tn * kBN2;
-      const uint4 bias8 = epilogue_bias8(p, n0, lane);  // in flight while the MMAs finish
+      const BiasRef bias8 = epilogue_bias8(p, n0, lane);  // in flight while the MMAs finish
       if (!mbar_wait_bounded(&tmem_full[acc], acc_phase, abort_flag)) break;
       tc_fence_after();
       epilogue_warp_pipelined<EPI>(p, tmem_base + acc * kBN2 + ((uint32_t)(quad * 32) << 16),
@@ -396,7 +396,7 @@ gemm_tcgen05_2cta_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
       if (h >= w.halves) continue;
       const int m0 = w.tm * kBM2 + (int)cta_rank * 128;
       const int n0 = w.n0 + h * 256;
-      const uint4 bias8 = epilogue_bias8(p, n0, lane);  // in flight while the MMAs finish
+      const BiasRef bias8 = epilogue_bias8(p, n0, lane);  // in flight while the MMAs finish
       if (!mbar_wait_bounded(&tmem_full[h], uses & 1u, abort_flag)) break;
       ++uses;
       tc_fence_after();
