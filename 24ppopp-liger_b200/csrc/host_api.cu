@@ -31,7 +31,7 @@ struct liger_model {
   std::vector<cudaEvent_t> ev_pool;                      // reusable events
   std::vector<std::pair<int, std::pair<cudaEvent_t, cudaEvent_t>>> ev_rec;  // (name, (before, after))
   cudaStream_t copy_in = nullptr, copy_out = nullptr;  // host-buffer entry point: copies overlapped with the first / last kernels
-  cudaEvent_t ev_io[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+  cudaEvent_t ev_io[9] = {};
   bool timeline = false;  // record per-kernel events in interleaved passes too (diagnostics)
   struct TimelineRec { int name, stream; cudaEvent_t e0, e1; };
   std::vector<TimelineRec> tl_rec;
@@ -315,15 +315,16 @@ extern "C" int liger_model_set_micro_batches(liger_model* m, int micro_batches) 
   return LIGER_OK;
 }
 
-// world_size == 1, even batch: the two halves of the batch are uploaded one after the other and the
-// first kernels (input LayerNorm, QKV GEMM) run per half, so that the second upload hides behind the
-// first half's GEMM; likewise the last GEMM runs per half and the first half's download hides behind
-// the second half's GEMM.  Rows are independent in those kernels, so the result is bit for bit the
-// one of the un-split launch.  Returns the number of launches, or 0 if this form does not apply.
+// world_size == 1: the batch is uploaded in `parts` pieces (4, 2 or 1: the largest that divides it) one after
+// the other and the first kernels (input LayerNorm, QKV GEMM) run per piece, so that every upload but the first
+// hides behind the previous piece's GEMM; likewise the last GEMM runs per piece and every download but the last
+// hides behind the next piece's GEMM.  Rows are independent in those kernels, so the result is bit for bit
+// the one of the un-split launch.  Returns the number of launches, or 0 if this form does not apply.
 static int forward_host_pipelined(liger_model* m, const void* host_input, void* host_output, int batch, int seq_len, int slot,
                                   cudaStream_t s) {
   Bert_Model& b = *m->model;
-  if (m->timing || (batch & 1) || m->sp.world_size != 1) return 0;
+  const int parts = batch % 4 == 0 ? 4 : batch % 2 == 0 ? 2 : 1;
+  if (m->timing || parts == 1 || m->sp.world_size != 1) return 0;
   std::vector<FuncWrap> vec = b.forward(m->io_in, m->io_out, batch, seq_len, slot);
   const bool ln_first = vec.size() >= 2 && vec[0].name == kPrologueName && vec[1].type == GEMM && vec[1].name == 0;
   const size_t first_gemm = ln_first ? 1 : 0;
@@ -337,19 +338,21 @@ static int forward_host_pipelined(liger_model* m, const void* host_input, void* 
     LIGER_CUDA_TRY(cudaStreamCreateWithFlags(&m->copy_out, cudaStreamNonBlocking));
     for (auto& e : m->ev_io) LIGER_CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
   }
-  const int hb = batch / 2, rows = hb * seq_len, H = b.H;
-  const size_t half_bytes = (size_t)rows * H * 2;
+  const int pb = batch / parts, rows = pb * seq_len, H = b.H;
+  const size_t part_bytes = (size_t)rows * H * 2;
   const char* hin = (const char*)host_input;
   char* hout = (char*)host_output;
+  cudaEvent_t* ev_start = &m->ev_io[0];  // [0]: caller's position; [1..4]: piece uploaded; [5..7]: piece computed; [8]: downloads done
   // uploads: ordered after everything the caller has queued (the previous step may still read io_in)
-  LIGER_CUDA_TRY(cudaEventRecord(m->ev_io[0], s));
-  LIGER_CUDA_TRY(cudaStreamWaitEvent(m->copy_in, m->ev_io[0], 0));
-  LIGER_CUDA_TRY(cudaMemcpyAsync(m->io_in, hin, half_bytes, cudaMemcpyHostToDevice, m->copy_in));
-  LIGER_CUDA_TRY(cudaEventRecord(m->ev_io[1], m->copy_in));
-  LIGER_CUDA_TRY(cudaMemcpyAsync((char*)m->io_in + half_bytes, hin + half_bytes, half_bytes, cudaMemcpyHostToDevice, m->copy_in));
-  LIGER_CUDA_TRY(cudaEventRecord(m->ev_io[2], m->copy_in));
+  LIGER_CUDA_TRY(cudaEventRecord(ev_start[0], s));
+  LIGER_CUDA_TRY(cudaStreamWaitEvent(m->copy_in, ev_start[0], 0));
+  for (int h = 0; h < parts; ++h) {
+    LIGER_CUDA_TRY(cudaMemcpyAsync((char*)m->io_in + h * part_bytes, hin + h * part_bytes, part_bytes, cudaMemcpyHostToDevice,
+                                   m->copy_in));
+    LIGER_CUDA_TRY(cudaEventRecord(m->ev_io[1 + h], m->copy_in));
+  }
   int n = 0, rc;
-  for (int h = 0; h < 2; ++h) {
+  for (int h = 0; h < parts; ++h) {
     LIGER_CUDA_TRY(cudaStreamWaitEvent(s, m->ev_io[1 + h], 0));
     if (ln_first) {
       const LayerNorm* ln = b.encoders[0]->ln_mha;
@@ -361,7 +364,7 @@ static int forward_host_pipelined(liger_model* m, const void* host_input, void* 
     GEMM_ARGS a = g0;
     a.m = rows;
     a.a = (const half_t*)g0.a + (size_t)h * rows * g0.lda;
-    const size_t head_off = (size_t)h * hb * g0.heads * seq_len * g0.head_dim;  // [B, h, S, D]: the batch is the outer dimension
+    const size_t head_off = (size_t)h * pb * g0.heads * seq_len * g0.head_dim;  // [B, h, S, D]: the batch is the outer dimension
     a.q_out = (half_t*)g0.q_out + head_off;
     a.k_out = (half_t*)g0.k_out + head_off;
     a.v_out = (half_t*)g0.v_out + head_off;
@@ -374,7 +377,7 @@ static int forward_host_pipelined(liger_model* m, const void* host_input, void* 
     if ((rc = vec[i].callback(dp)) != LIGER_OK) return rc;
     ++n;
   }
-  for (int h = 0; h < 2; ++h) {
+  for (int h = 0; h < parts; ++h) {
     GEMM_ARGS a = gl;
     a.m = rows;
     a.a = (const half_t*)gl.a + (size_t)h * rows * gl.lda;
@@ -382,15 +385,17 @@ static int forward_host_pipelined(liger_model* m, const void* host_input, void* 
     if (gl.residual) a.residual = (const half_t*)gl.residual + (size_t)h * rows * gl.ldr;
     if ((rc = liger_gemm_fp16(&a, s)) != LIGER_OK) return rc;
     ++n;
-    if (h == 0) {
-      LIGER_CUDA_TRY(cudaEventRecord(m->ev_io[3], s));
-      LIGER_CUDA_TRY(cudaStreamWaitEvent(m->copy_out, m->ev_io[3], 0));
-      LIGER_CUDA_TRY(cudaMemcpyAsync(hout, m->io_out, half_bytes, cudaMemcpyDeviceToHost, m->copy_out));
-      LIGER_CUDA_TRY(cudaEventRecord(m->ev_io[4], m->copy_out));
+    if (h + 1 < parts) {
+      LIGER_CUDA_TRY(cudaEventRecord(m->ev_io[5 + h], s));
+      LIGER_CUDA_TRY(cudaStreamWaitEvent(m->copy_out, m->ev_io[5 + h], 0));
+      LIGER_CUDA_TRY(cudaMemcpyAsync(hout + h * part_bytes, (char*)m->io_out + h * part_bytes, part_bytes, cudaMemcpyDeviceToHost,
+                                     m->copy_out));
     }
   }
-  LIGER_CUDA_TRY(cudaMemcpyAsync(hout + half_bytes, (char*)m->io_out + half_bytes, half_bytes, cudaMemcpyDeviceToHost, s));
-  LIGER_CUDA_TRY(cudaStreamWaitEvent(s, m->ev_io[4], 0));  // the caller's stream covers the first half's download too
+  LIGER_CUDA_TRY(cudaEventRecord(m->ev_io[8], m->copy_out));
+  LIGER_CUDA_TRY(cudaMemcpyAsync(hout + (parts - 1) * part_bytes, (char*)m->io_out + (parts - 1) * part_bytes, part_bytes,
+                                 cudaMemcpyDeviceToHost, s));
+  LIGER_CUDA_TRY(cudaStreamWaitEvent(s, m->ev_io[8], 0));  // the caller's stream covers the earlier pieces' downloads too
   return n;
 }
 
