@@ -102,6 +102,7 @@ SIGNATURES = {
     "liger_model_forward_host": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "liger_model_set_mask": (_I, [_P, _P]),
     "liger_model_set_micro_batches": (_I, [_P, _I]),
+    "liger_model_set_output_sharding": (_I, [_P, _I]),
     "liger_model_decode": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "liger_model_fill_kv_cache": (_I, [_P]),
     "liger_model_timeline": (_I, [_P, _I, _I, C.POINTER(_I), C.POINTER(_I), C.POINTER(C.c_double), C.POINTER(C.c_double)]),

@@ -23,6 +23,7 @@ struct liger_model {
   int device = 0;
   bool timing = false;
   int micro_batches = 1;
+  bool shard_output = false;  // forward_host with world_size > 1: every rank downloads its own rows
   std::vector<cudaStream_t> aux_streams;
   cudaEvent_t ev_fork = nullptr;
   std::vector<cudaEvent_t> ev_join;
@@ -309,6 +310,12 @@ extern "C" int liger_model_fill_kv_cache(liger_model* m) {
   }
 }
 
+extern "C" int liger_model_set_output_sharding(liger_model* m, int sharded) {
+  if (!m) return liger::set_error(LIGER_ERR_INVALID, "model_set_output_sharding: null model");
+  m->shard_output = sharded != 0;
+  return LIGER_OK;
+}
+
 extern "C" int liger_model_set_micro_batches(liger_model* m, int micro_batches) {
   if (!m || micro_batches < 1 || micro_batches > 8) return liger::set_error(LIGER_ERR_INVALID, "model_set_micro_batches: 1..8");
   m->micro_batches = micro_batches;
@@ -435,7 +442,13 @@ extern "C" int liger_model_forward_host(liger_model* m, const void* host_input, 
   if (rc != LIGER_OK) return rc;
   const int n = liger_model_forward(m, w.xbuf, m->io_out, batch, seq_len, slot, stream);
   if (n < 0) return n;
-  if (rank == 0) LIGER_CUDA_TRY(cudaMemcpyAsync(host_output, m->io_out, bytes, cudaMemcpyDeviceToHost, s));
+  if (m->shard_output) {
+    if (hi > lo)
+      LIGER_CUDA_TRY(cudaMemcpyAsync((half_t*)host_output + (size_t)lo * H, m->io_out + (size_t)lo * H, (size_t)(hi - lo) * H * 2,
+                                     cudaMemcpyDeviceToHost, s));
+  } else if (rank == 0) {
+    LIGER_CUDA_TRY(cudaMemcpyAsync(host_output, m->io_out, bytes, cudaMemcpyDeviceToHost, s));
+  }
   return n + 1;
 }
 

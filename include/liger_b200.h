@@ -393,6 +393,13 @@ LIGER_API int liger_model_fill_kv_cache(liger_model* model);
  */
 LIGER_API int liger_model_set_micro_batches(liger_model* model, int micro_batches);
 
+/* world_size > 1, liger_model_forward_host only.  sharded = 1: every rank copies rows
+ * [rank * ceil(M / world_size), ...) of the result -- the rows it uploaded -- to the same offsets of ITS
+ * host_output, so that ranks whose host_output is one shared, pinned host buffer fill it together and each
+ * PCIe link carries 1/world_size of the result.  sharded = 0 (default): rank 0 downloads everything.
+ * (No counterpart in the reference.) */
+LIGER_API int liger_model_set_output_sharding(liger_model* model, int sharded);
+
 /* Diagnostics for interleaved passes: with enable != 0 the next interleaved pass records an event
  * before and after every kernel on its own stream; a later call returns, for the last such pass,
  * kernel name, stream index and the enqueue-order event times in ms since the pass started (up to
@@ -405,7 +412,9 @@ LIGER_API int liger_model_timeline(liger_model* model, int enable, int capacity,
  * reading host_output).  world_size == 1: the whole input is copied to the device and the whole
  * result back.  world_size > 1: every rank passes the same full host input but uploads only its
  * own 1/world_size of the rows, which an all-gather over peer memory completes on every GPU; the
- * result is copied to host_output on rank 0 only (other ranks leave host_output untouched). */
+ * result is copied to host_output on rank 0 only (other ranks leave host_output untouched), unless
+ * liger_model_set_output_sharding() asked for every rank to download its own rows.
+ * (No counterpart in the reference, whose buffers never leave the device: src/test_schedule.h:19-47.) */
 LIGER_API int liger_model_forward_host(liger_model* model, const void* host_input, void* host_output, int batch,
                                        int seq_len, int slot, void* stream);
 /*
