@@ -138,6 +138,17 @@ def _tp_worker(rank, world, port, case, results):
     torch.cuda.synchronize()
     if rank == 0:
         assert torch.equal(hout, out.cpu())
+    # sharded download: every rank receives exactly the rows it uploaded, nothing else is written
+    liger.check(lib.liger_model_set_output_sharding(model, 1))
+    hpart = torch.zeros((M, H), dtype=torch.float16).pin_memory()
+    liger.check(lib.liger_model_forward_host(model, C.c_void_p(hin.data_ptr()), C.c_void_p(hpart.data_ptr()), c["B"], c["S"],
+                                             1, stream_ptr()))
+    torch.cuda.synchronize()
+    rpr = (M + world - 1) // world
+    lo, hi = min(rank * rpr, M), min((rank + 1) * rpr, M)
+    assert torch.equal(hpart[lo:hi], out.cpu()[lo:hi])
+    assert not hpart[:lo].any() and not hpart[hi:].any()
+    liger.check(lib.liger_model_set_output_sharding(model, 0))
     # the batch split into two interleaved micro-requests gives the same bits
     if c["B"] % 2 == 0:
         liger.check(lib.liger_model_set_micro_batches(model, 2))
