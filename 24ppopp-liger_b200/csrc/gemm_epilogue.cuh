@@ -69,16 +69,6 @@ constexpr uint64_t kL2EvictLast = 0x14F0000000000000ull;
 constexpr uint64_t kL2EvictNormal = 0x1000000000000000ull;
 
 // ---- epilogue helpers -------------------------------------------------------------------------
-__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
-  const __half2* h = reinterpret_cast<const __half2*>(&u);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 t = __half22float2(h[i]);
-    f[2 * i] = t.x;
-    f[2 * i + 1] = t.y;
-  }
-}
-
 // 32 accumulator columns [col0, col0+32) of one row -> bias / activation -> 32 fp16 values in o[4].
 __device__ __forceinline__ void epilogue_math(const GemmParams& p, int row, int col0, const uint32_t (&r)[32],
                                               uint4 (&o)[4]) {

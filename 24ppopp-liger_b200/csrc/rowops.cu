@@ -31,52 +31,34 @@ layernorm_kernel(const __half* __restrict__ x_in, const __half* __restrict__ res
   const int row = blockIdx.x;
   const int nvec = n >> 3;
   const size_t base = (size_t)row * n;
-  float v[kLnMaxVec][8];
+  // The row stays in registers as the fp16 values it is (8 per uint4) and is widened on the fly in each of
+  // the three passes: half the registers of an fp32 copy, twice the resident CTAs, same arithmetic.
+  uint4 v[kLnMaxVec];
   float sum = 0.0f;
 #pragma unroll
   for (int i = 0; i < kLnMaxVec; ++i) {
     const int idx = threadIdx.x + i * kLnThreads;
     if (idx < nvec) {
-      uint4 u = *reinterpret_cast<const uint4*>(x_in + base + (size_t)idx * 8);
-      const __half2* h = reinterpret_cast<const __half2*>(&u);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float2 f = __half22float2(h[j]);
-        v[i][2 * j] = f.x;
-        v[i][2 * j + 1] = f.y;
-      }
+      v[i] = *reinterpret_cast<const uint4*>(x_in + base + (size_t)idx * 8);
       if (kResidual) {
-        uint4 r = __ldg(reinterpret_cast<const uint4*>(res_in + base + (size_t)idx * 8));
-        const __half2* rh = reinterpret_cast<const __half2*>(&r);
-        float b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        if (bias != nullptr) {
-          uint4 bu = __ldg(reinterpret_cast<const uint4*>(bias + (size_t)idx * 8));
-          const __half2* bh = reinterpret_cast<const __half2*>(&bu);
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float2 f = __half22float2(bh[j]);
-            b[2 * j] = f.x;
-            b[2 * j + 1] = f.y;
-          }
-        }
-        uint4 o;
-        uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+        float x[8], r[8], b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        unpack8(v[i], x);
+        unpack8(__ldg(reinterpret_cast<const uint4*>(res_in + base + (size_t)idx * 8)), r);
+        if (bias != nullptr) unpack8(__ldg(reinterpret_cast<const uint4*>(bias + (size_t)idx * 8)), b);
+        uint32_t* ow = reinterpret_cast<uint32_t*>(&v[i]);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          float2 f = __half22float2(rh[j]);
-          float t0 = f.x + v[i][2 * j] + b[2 * j];
-          float t1 = f.y + v[i][2 * j + 1] + b[2 * j + 1];
+          const float t0 = r[2 * j] + x[2 * j] + b[2 * j];
+          const float t1 = r[2 * j + 1] + x[2 * j + 1] + b[2 * j + 1];
           sum += t0 + t1;
-          __half2 hh = __floats2half2_rn(t0, t1);
-          ow[j] = *reinterpret_cast<uint32_t*>(&hh);
-          float2 back = __half22float2(hh);
-          v[i][2 * j] = back.x;
-          v[i][2 * j + 1] = back.y;
+          ow[j] = pack_half2(t0, t1);  // stored in fp16 and used from here on as the fp16 value
         }
-        *reinterpret_cast<uint4*>(out_sum + base + (size_t)idx * 8) = o;
+        *reinterpret_cast<uint4*>(out_sum + base + (size_t)idx * 8) = v[i];
       } else {
+        float x[8];
+        unpack8(v[i], x);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) sum += v[i][j];
+        for (int j = 0; j < 8; ++j) sum += x[j];
       }
     }
   }
@@ -87,9 +69,11 @@ layernorm_kernel(const __half* __restrict__ x_in, const __half* __restrict__ res
   for (int i = 0; i < kLnMaxVec; ++i) {
     const int idx = threadIdx.x + i * kLnThreads;
     if (idx < nvec) {
+      float x[8];
+      unpack8(v[i], x);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        float d = v[i][j] - mean;
+        const float d = x[j] - mean;
         vs += d * d;
       }
     }
@@ -99,18 +83,15 @@ layernorm_kernel(const __half* __restrict__ x_in, const __half* __restrict__ res
   for (int i = 0; i < kLnMaxVec; ++i) {
     const int idx = threadIdx.x + i * kLnThreads;
     if (idx < nvec) {
-      uint4 gu = __ldg(reinterpret_cast<const uint4*>(gamma + (size_t)idx * 8));
-      uint4 bu = __ldg(reinterpret_cast<const uint4*>(beta + (size_t)idx * 8));
-      const __half2* gh = reinterpret_cast<const __half2*>(&gu);
-      const __half2* bh = reinterpret_cast<const __half2*>(&bu);
+      float x[8], g[8], b[8];
+      unpack8(v[i], x);
+      unpack8(__ldg(reinterpret_cast<const uint4*>(gamma + (size_t)idx * 8)), g);
+      unpack8(__ldg(reinterpret_cast<const uint4*>(beta + (size_t)idx * 8)), b);
       uint4 o;
       uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float2 g = __half22float2(gh[j]);
-        float2 b = __half22float2(bh[j]);
-        ow[j] = pack_half2((v[i][2 * j] - mean) * rstd * g.x + b.x, (v[i][2 * j + 1] - mean) * rstd * g.y + b.y);
-      }
+      for (int j = 0; j < 4; ++j)
+        ow[j] = pack_half2((x[2 * j] - mean) * rstd * g[2 * j] + b[2 * j], (x[2 * j + 1] - mean) * rstd * g[2 * j + 1] + b[2 * j + 1]);
       *reinterpret_cast<uint4*>(y + base + (size_t)idx * 8) = o;
     }
   }
