@@ -255,15 +255,23 @@ __device__ __forceinline__ void stage_writeout64(const GemmParams& p, uint8_t* s
     const size_t S = cache ? (size_t)p.kv_stride : (size_t)p.seq_len;
     __half* base = (which == 0 ? p.qkv[0] : which == 1 ? p.qkv[1] : p.qkv[2]) +
                    ((size_t)head * S + (cache ? (size_t)p.kv_pos : 0)) * p.head_dim + d;
-    int b = row / p.seq_len, s = row - b * p.seq_len;
+    // rows advance by 4: the destination moves by 4 tokens inside a sequence and jumps to the next
+    // batch entry's block when the sequence ends
+    const int b = row / p.seq_len;
+    int s = row - b * p.seq_len;
+    const size_t batch_step = (size_t)p.heads * S * p.head_dim;
+    __half* dst = base + (size_t)b * batch_step + (size_t)s * p.head_dim;
+    const int row_step = 4 * p.head_dim;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-      if (row < p.m)
-        *reinterpret_cast<uint4*>(base + ((size_t)b * p.heads * S + (size_t)s) * p.head_dim) =
-            *stage_slot<64>(stage, rsub + i * 4, ch);
+      if (row < p.m) *reinterpret_cast<uint4*>(dst) = *stage_slot<64>(stage, rsub + i * 4, ch);
       row += 4;
       s += 4;
-      while (s >= p.seq_len) { s -= p.seq_len; ++b; }
+      dst += row_step;
+      while (s >= p.seq_len) {
+        s -= p.seq_len;
+        dst += batch_step - (size_t)p.seq_len * p.head_dim;
+      }
     }
   } else if constexpr (EPI == LIGER_EPI_SCATTER) {
     int owner = row / p.rows_per_rank, lr = row - owner * p.rows_per_rank;
