@@ -70,6 +70,7 @@ SIGNATURES = {
     "liger_version": (C.c_char_p, []),
     "liger_device_status": (_I, [C.POINTER(C.c_uint * 4)]),
     "liger_device_status_clear": (_I, []),
+    "liger_set_wait_budget_ms": (_I, [_I]),
     "liger_fill_normal": (_I, [_P, _I, _I, _I, _I, _I, _I, _U32, _U32, _F, _F, _I, _P]),
     "liger_gemm_fp16": (_I, [C.POINTER(GemmArgs), _P]),
     "liger_transpose_weight": (_I, [_P, _P, _I, _I, _I, _P]),
@@ -92,6 +93,8 @@ SIGNATURES = {
     "liger_comm_timing": (_I, [_P, _I, _I, C.POINTER(C.c_double * 4)]),
     "liger_comm_rank": (_I, [_P]),
     "liger_comm_world_size": (_I, [_P]),
+    "liger_comm_channels": (_I, [_P]),
+    "liger_allgather_ce": (_I, [_P, _I, _SZ, _I, _I, _I, _I, _P]),
     "liger_allreduce_ce": (_I, [_P, _I, _SZ, _SZ, _SZ, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "liger_allreduce_fused": (_I, [_P, _I, _SZ, _SZ, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "liger_model_config_init": (None, [C.POINTER(ModelConfig)]),
@@ -102,6 +105,8 @@ SIGNATURES = {
     "liger_model_forward_host": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "liger_model_set_mask": (_I, [_P, _P]),
     "liger_model_set_micro_batches": (_I, [_P, _I]),
+    "liger_model_set_overlap": (_I, [_P, _I]),
+    "liger_model_overlap_times": (_I, [_P, C.POINTER(C.c_double * 4)]),
     "liger_model_set_output_sharding": (_I, [_P, _I]),
     "liger_model_decode": (_I, [_P, _P, _P, _I, _I, _I, _P]),
     "liger_model_fill_kv_cache": (_I, [_P]),

@@ -395,8 +395,12 @@ extern "C" int liger_attention_decode(const void* q, const void* k_cache, const 
                                       void* stream) {
   if (!q || !k_cache || !v_cache || !out || !scratch || batch <= 0 || heads <= 0 || kv_len <= 0 || kv_stride < kv_len)
     return set_error(LIGER_ERR_INVALID, "attention_decode: bad argument");
+  if (head_dim <= 0 || ldo < heads * head_dim)
+    return set_error(LIGER_ERR_INVALID, "attention_decode: ldo = %d must be >= heads * head_dim = %d", ldo, heads * head_dim);
   if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15u)
     return set_error(LIGER_ERR_INVALID, "attention_decode: q / caches must be 16-byte aligned");
+  if (((uintptr_t)scratch & 3u) || ((uintptr_t)out & 1u))
+    return set_error(LIGER_ERR_INVALID, "attention_decode: scratch must be 4-byte aligned, out 2-byte aligned");
   if (batch > 65535 || heads > 65535) return set_error(LIGER_ERR_UNSUPPORTED, "attention_decode: batch, heads <= 65535");
   if (!current_device()) return LIGER_ERR_CUDA;
   cudaStream_t s = (cudaStream_t)stream;
@@ -467,6 +471,10 @@ extern "C" int liger_attention_decode_noalloc(const void* q, const void* k_cache
     return set_error(LIGER_ERR_INVALID, "attention_decode_noalloc: bad argument");
   if (head_dim != 64 && head_dim != 128)
     return set_error(LIGER_ERR_UNSUPPORTED, "attention_decode_noalloc: head_dim %d (64 and 128 are implemented)", head_dim);
+  if (ldo < heads * head_dim)
+    return set_error(LIGER_ERR_INVALID, "attention_decode_noalloc: ldo = %d must be >= heads * head_dim = %d", ldo,
+                     heads * head_dim);
+  if ((uintptr_t)out & 1u) return set_error(LIGER_ERR_INVALID, "attention_decode_noalloc: out must be 2-byte aligned");
   if (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15u)
     return set_error(LIGER_ERR_INVALID, "attention_decode_noalloc: q / caches must be 16-byte aligned");
   if (batch > 65535 || heads > 65535) return set_error(LIGER_ERR_UNSUPPORTED, "attention_decode_noalloc: batch, heads <= 65535");

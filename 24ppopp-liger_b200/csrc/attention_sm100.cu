@@ -28,6 +28,8 @@
 // Every wait is bounded.
 #include "runtime.h"
 
+LIGER_REGISTER_WAIT_BUDGET()
+
 namespace liger {
 
 namespace {

@@ -19,6 +19,8 @@
 #include "comm_internal.h"
 #include "runtime.h"
 
+LIGER_REGISTER_WAIT_BUDGET()
+
 namespace liger {
 
 constexpr int kFlagStrideWords = 32;        // one 128-byte line per (channel, peer) flag
@@ -72,7 +74,7 @@ __device__ __forceinline__ bool barrier_wait(const CommDev& c, int channel, uint
     const unsigned long long t0 = globaltimer_ns();
     uint32_t spins = 0;
     while ((int32_t)(ld_acquire_sys(f) - epoch) < 0) {
-      if ((++spins & 0xffu) == 0 && globaltimer_ns() - t0 > kWaitBudgetNs) {
+      if ((++spins & 0xffu) == 0 && globaltimer_ns() - t0 > g_wait_budget_ns) {
         *s_fail = 1;
         report_failure(st, LIGER_DEV_TIMEOUT, where, (unsigned)threadIdx.x, epoch);
         break;
@@ -133,10 +135,11 @@ allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t recv_o
       int p = first + kx;
       if (p >= c.ws) p -= c.ws;
       // mode 3: the producing GEMMs already stored every rank's rows for this owner into local slots
+      // mode 5: the same input, but the finished rows are stored locally only (a copy-engine all-gather follows)
       // mode 4: peers' rows were copied into local receive slots by the copy engines; own rows are
       // read from the own partial in place
       const __half* src =
-          one_shot == 3 ? reinterpret_cast<const __half*>(c.base[c.rank] + partial_off) +
+          (one_shot == 3 || one_shot == 5) ? reinterpret_cast<const __half*>(c.base[c.rank] + partial_off) +
                               ((size_t)p * rows_per_rank + (row - c.rank * rows_per_rank)) * n
           : one_shot == 4
               ? (p == c.rank ? reinterpret_cast<const __half*>(c.base[c.rank] + partial_off) + roff
@@ -237,7 +240,7 @@ allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t recv_o
 #pragma unroll
           for (int j = 0; j < 4; ++j) ow[j] = pack_half2(v[i][2 * j], v[i][2 * j + 1]);
         }
-        if (one_shot == 1 || one_shot == 4) {
+        if (one_shot == 1 || one_shot == 4 || one_shot == 5) {
           *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(c.base[c.rank] + out_off) + roff + (size_t)idx * 8) = o;
         } else {
           for (int kx = 0; kx < c.ws; ++kx) {
@@ -277,6 +280,11 @@ allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t recv_o
 }  // namespace liger
 
 using namespace liger;
+
+namespace liger {
+__global__ void comm_barrier_kernel(CommDev c, int channel, uint32_t epoch, unsigned long long* stamps, int stamp_slot,
+                                    DeviceStatus* st, unsigned int where);
+}
 
 extern "C" int liger_comm_create(liger_comm** out, int rank, int world_size, size_t data_bytes, int channels) {
   if (!out || world_size < 1 || world_size > kMaxRanks || rank < 0 || rank >= world_size || channels < 1 ||
@@ -406,7 +414,7 @@ extern "C" int liger_allreduce_fused(liger_comm* c, int channel, size_t partial_
   if (row_begin < 0 || row_end > m || row_begin > row_end) return set_error(LIGER_ERR_INVALID, "allreduce_fused: bad row range");
   const size_t bytes = (size_t)m * n * 2;
   const int rpr_all = (m + c->ws - 1) / c->ws;
-  const size_t in_bytes = one_shot == 3 ? (size_t)c->ws * rpr_all * n * 2 : bytes;
+  const size_t in_bytes = (one_shot == 3 || one_shot == 5) ? (size_t)c->ws * rpr_all * n * 2 : bytes;
   if (partial_off % 16 || out_off % 16 || partial_off + in_bytes > c->data_bytes || out_off + bytes > c->data_bytes)
     return set_error(LIGER_ERR_INVALID, "allreduce_fused: offsets must be 16-byte aligned and inside the %zu-byte data region",
                      c->data_bytes);
@@ -419,7 +427,8 @@ extern "C" int liger_allreduce_fused(liger_comm* c, int channel, size_t partial_
   CommDev cd;
   for (int p = 0; p < kMaxRanks; ++p) cd.base[p] = p < c->ws ? c->peer[p] : nullptr;
   cd.rank = c->rank; cd.ws = c->ws;
-  if (one_shot < 0 || one_shot > 3) return set_error(LIGER_ERR_INVALID, "allreduce_fused: one_shot must be 0, 1, 2 or 3");
+  if (one_shot < 0 || one_shot > 5 || one_shot == 4)
+    return set_error(LIGER_ERR_INVALID, "allreduce_fused: one_shot must be 0, 1, 2, 3 or 5");
   int lo = row_begin, hi = row_end;
   if (one_shot != 1) {
     const int rpr = (m + c->ws - 1) / c->ws;
@@ -440,11 +449,14 @@ extern "C" int liger_allreduce_fused(liger_comm* c, int channel, size_t partial_
     const char* e = getenv("LIGER_AR_MAX_CTAS");
     max_ctas = (e && atoi(e) > 0) ? atoi(e) : 0;
   }
-  const int cap = max_ctas > 0 ? max_ctas : (64 * kMaxRanks / c->ws < dev->sm_count * 4 ? 64 * kMaxRanks / c->ws : dev->sm_count * 4);
+  // Mode 5 touches local memory only and is meant to run with the SMs to itself: no cap below the machine.
+  const int cap = one_shot == 5 ? dev->sm_count * 4
+                  : max_ctas > 0 ? max_ctas
+                                 : (64 * kMaxRanks / c->ws < dev->sm_count * 4 ? 64 * kMaxRanks / c->ws : dev->sm_count * 4);
   if (grid > cap) grid = cap;
   if (grid < 1) grid = 1;
   const uint32_t e_in = ++c->epoch[channel];
-  const uint32_t e_out = ++c->epoch[channel];
+  const uint32_t e_out = one_shot == 5 ? e_in : ++c->epoch[channel];  // mode 5 has no exit barrier
   allreduce_entry_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(cd, channel, e_in, c->stamps + 8 * channel,
                                                                      dev->status_dev);
   int rc = check_launch("allreduce_entry_barrier_kernel");
@@ -452,8 +464,44 @@ extern "C" int liger_allreduce_fused(liger_comm* c, int channel, size_t partial_
   allreduce_fused_kernel<<<grid, kArThreads, 0, (cudaStream_t)stream>>>(
       cd, channel, kFlagRegionBytes + partial_off, 0, kFlagRegionBytes + out_off, (const __half*)residual_in, (__half*)hidden, (const __half*)bias,
       (const __half*)gamma, (const __half*)beta, n, lo, hi, one_shot, rpr_all, e_in, e_out, c->done + channel,
-      c->stamps + 8 * channel, dev->status_dev, 0);
+      c->stamps + 8 * channel, dev->status_dev, one_shot == 5 ? 1 : 0);
   return check_launch("allreduce_fused_kernel");
+}
+
+extern "C" int liger_comm_channels(liger_comm* c) { return c ? c->channels : 0; }
+
+// All-gather of finished rows by the copy engines: this rank's own rows of the [m, n] tensor at out_off go to the
+// same place in every peer's segment, then a one-warp barrier kernel on `channel` tells every rank that all rows
+// have landed.  No SM takes part in the transfer, so it runs under whatever kernels another stream has in flight.
+extern "C" int liger_allgather_ce(liger_comm* c, int channel, size_t out_off, int m, int n, int row_begin, int row_end,
+                                  void* stream) {
+  if (!c) return set_error(LIGER_ERR_INVALID, "allgather_ce: null communicator");
+  if (!c->connected) return set_error(LIGER_ERR_COMM, "allgather_ce: communicator is not connected");
+  if (channel < 0 || channel >= c->channels) return set_error(LIGER_ERR_INVALID, "allgather_ce: channel %d of %d", channel, c->channels);
+  if (m <= 0 || n <= 0 || n % 8) return set_error(LIGER_ERR_INVALID, "allgather_ce: n = %d must be a positive multiple of 8", n);
+  if (row_begin < 0 || row_end > m || row_begin > row_end) return set_error(LIGER_ERR_INVALID, "allgather_ce: bad row range");
+  if (out_off % 16 || out_off + (size_t)m * n * 2 > c->data_bytes)
+    return set_error(LIGER_ERR_INVALID, "allgather_ce: region must be 16-byte aligned and inside the %zu-byte data region", c->data_bytes);
+  const DeviceInfo* dev = current_device();
+  if (!dev) return LIGER_ERR_CUDA;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int ws = c->ws, rank = c->rank, rpr = (m + ws - 1) / ws;
+  int lo = rank * rpr > row_begin ? rank * rpr : row_begin;
+  const int own_hi = (rank + 1) * rpr < m ? (rank + 1) * rpr : m;
+  int hi = own_hi < row_end ? own_hi : row_end;
+  if (hi < lo) hi = lo;
+  for (int k = 1; k < ws && hi > lo; ++k) {
+    const int p = (rank + k) % ws;
+    LIGER_CUDA_TRY(cudaMemcpyAsync(c->peer[p] + kFlagRegionBytes + out_off + (size_t)lo * n * 2,
+                                   c->local + kFlagRegionBytes + out_off + (size_t)lo * n * 2, (size_t)(hi - lo) * n * 2,
+                                   cudaMemcpyDefault, s));
+  }
+  CommDev cd;
+  for (int p = 0; p < kMaxRanks; ++p) cd.base[p] = p < ws ? c->peer[p] : nullptr;
+  cd.rank = rank; cd.ws = ws;
+  const uint32_t e = ++c->epoch[channel];
+  comm_barrier_kernel<<<1, 32, 0, s>>>(cd, channel, e, c->stamps + 8 * channel, 6, dev->status_dev, 0x212u);
+  return check_launch("comm_barrier_kernel");
 }
 
 // ---- the same collective with the data movement on the copy engines ------------------------------------
@@ -493,6 +541,8 @@ extern "C" int liger_allreduce_ce(liger_comm* c, int channel, size_t partial_off
     return set_error(LIGER_ERR_INVALID, "allreduce_ce: regions must be 16-byte aligned and inside the %zu-byte data region", c->data_bytes);
   if ((gamma == nullptr) != (beta == nullptr)) return set_error(LIGER_ERR_INVALID, "allreduce_ce: gamma and beta go together");
   if (hidden && !residual_in) residual_in = hidden;
+  if (((uintptr_t)hidden | (uintptr_t)residual_in | (uintptr_t)bias | (uintptr_t)gamma | (uintptr_t)beta) & 15u)
+    return set_error(LIGER_ERR_INVALID, "allreduce_ce: pointers must be 16-byte aligned");
   const DeviceInfo* dev = current_device();
   if (!dev) return LIGER_ERR_CUDA;
   cudaStream_t s = (cudaStream_t)stream;

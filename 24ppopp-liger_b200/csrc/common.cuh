@@ -35,8 +35,13 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
   return t;
 }
 
-// Wall-clock budget of every device-side wait.
-constexpr unsigned long long kWaitBudgetNs = 2000000000ull;  // 2 s
+// Wall-clock budget of every device-side wait, in nanoseconds (default 2 s).  Without relocatable device
+// code every translation unit has its own copy; the ones that wait register a setter (runtime.h,
+// LIGER_REGISTER_WAIT_BUDGET) so that liger_set_wait_budget_ms() keeps all copies in step.  It is read only on
+// the slow path of a wait (after hundreds of failed polls).
+#pragma nv_diag_suppress 177
+static __device__ unsigned long long g_wait_budget_ns = 2000000000ull;
+#pragma nv_diag_default 177
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -87,7 +92,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
       const unsigned long long now = globaltimer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > kWaitBudgetNs) {
+      } else if (now - t0 > g_wait_budget_ns) {
         *abort_flag = 1u;
         return false;
       }

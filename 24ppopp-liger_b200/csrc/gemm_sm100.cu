@@ -19,6 +19,8 @@
 
 #include "gemm_epilogue.cuh"
 
+LIGER_REGISTER_WAIT_BUDGET()
+
 namespace liger {
 
 template <int BN, int STAGES>

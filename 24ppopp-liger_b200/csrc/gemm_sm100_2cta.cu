@@ -13,6 +13,8 @@
 
 #include "gemm_epilogue.cuh"
 
+LIGER_REGISTER_WAIT_BUDGET()
+
 namespace liger {
 
 constexpr int kBM2 = 256;  // rows per cluster tile (128 per CTA)

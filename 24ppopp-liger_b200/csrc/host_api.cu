@@ -33,6 +33,13 @@ struct liger_model {
   std::vector<std::pair<int, std::pair<cudaEvent_t, cudaEvent_t>>> ev_rec;  // (name, (before, after))
   cudaStream_t copy_in = nullptr, copy_out = nullptr;  // host-buffer entry point: copies overlapped with the first / last kernels
   cudaEvent_t ev_io[9] = {};
+  // Pipelined micro-batches (world_size > 1): every compute kernel of every micro-batch runs on pipe_compute in
+  // turn, the copy-engine all-gathers on pipe_comm underneath them.
+  int overlap = 1;  // 1: that schedule; 0: one stream per micro-batch with the in-kernel collective
+  cudaStream_t pipe_compute = nullptr, pipe_comm = nullptr;
+  cudaEvent_t ev_pipe_fork = nullptr, ev_pipe_join = nullptr;
+  std::vector<cudaEvent_t> ev_reduced, ev_gather;
+  double overlap_acc[4] = {0, 0, 0, 0};  // exposed-wait ms, waits, gather ms, gathers (see liger_model_overlap_times)
   bool timeline = false;  // record per-kernel events in interleaved passes too (diagnostics)
   struct TimelineRec { int name, stream; cudaEvent_t e0, e1; };
   std::vector<TimelineRec> tl_rec;
@@ -135,10 +142,43 @@ extern "C" int liger_model_create(liger_model** out, const liger_model_config* c
 }
 
 extern "C" int liger_model_destroy(liger_model* m) {
-  // Device memory of a model lives until the process exits, as in the reference (its layers have no
-  // destructors); only the host object is released here.
+  // Unlike the reference (whose layers have no destructors and never call cudaFree), a model gives back all
+  // device memory, streams and events it created.  Work it has queued is waited for first.
+  if (!m) return LIGER_OK;
+  cudaSetDevice(m->device);
+  cudaDeviceSynchronize();
+  delete m->model;
+  if (m->io_in) cudaFree(m->io_in);
+  if (m->io_out) cudaFree(m->io_out);
+  for (cudaStream_t s : m->aux_streams) cudaStreamDestroy(s);
+  for (cudaStream_t s : {m->copy_in, m->copy_out, m->pipe_compute, m->pipe_comm})
+    if (s) cudaStreamDestroy(s);
+  auto drop = [](cudaEvent_t e) { if (e) cudaEventDestroy(e); };
+  drop(m->ev_fork); drop(m->ev_pipe_fork); drop(m->ev_pipe_join); drop(m->tl_base);
+  for (auto* v : {&m->ev_join, &m->ev_chain, &m->ev_pool, &m->ev_reduced, &m->ev_gather})
+    for (cudaEvent_t e : *v) drop(e);
+  for (auto& r : m->ev_rec) { drop(r.second.first); drop(r.second.second); }
+  for (auto& r : m->tl_rec) { drop(r.e0); drop(r.e1); }
+  for (cudaEvent_t e : m->ev_io) drop(e);
   delete m;
+  cudaGetLastError();
   return LIGER_OK;
+}
+
+// Workspace slot(s) of a pass: an explicit slot is checked, -1 takes the next `need` consecutive slots in
+// round-robin order (wrapping to slot 0 when fewer than `need` remain).
+static int pick_slots(Bert_Model& b, int slot, int need, const char* who) {
+  const int size = (int)b.slots.size();
+  if (need > size) return liger::set_error(LIGER_ERR_INVALID, "%s: %d micro-batches need %d workspace slots, the model has %d", who, need, need, size);
+  if (slot < 0) {
+    if (b.next_slot + need > size) b.next_slot = 0;
+    slot = b.next_slot;
+    b.next_slot = (slot + need) % size;
+  }
+  if (slot + need > size)
+    return liger::set_error(LIGER_ERR_INVALID, "%s: %d micro-batch(es) from slot %d need %d workspace slots, the model has %d", who,
+                            need, slot, slot + need, size);
+  return slot;
 }
 
 // One request, kernels in order on one stream.
@@ -243,19 +283,139 @@ static int forward_interleaved(liger_model* m, const void* input, void* output, 
   return n;
 }
 
+// Pseudo kernel names of the pipelined pass's own timing records (beyond the nine real kernel names).
+constexpr int kWaitRecord = 9;    // compute stream blocked until a micro-batch's all-gather has landed
+constexpr int kGatherRecord = 10; // a copy-engine all-gather, timed on the communication stream
+
+// The batch split into `mb` micro-requests (consecutive groups of sequences, one workspace slot each) that share
+// ONE compute stream: their compute segments (QKV, attention, out-proj | FFN-up, FFN-down) run back to back in
+// turn, never two at a time, so no kernel ever competes for SMs.  Each all-reduce is split: its reduce-scatter
+// half already rode on the row-parallel GEMM's epilogue; the reduction (+ residual + LayerNorm) of the owned rows
+// runs on the compute stream as a short local kernel (all-reduce mode 5); its all-gather half goes to the copy
+// engines on the communication stream, underneath the other micro-request's next compute segment, which is several
+// times longer than the transfer.  The next segment of the same micro-request waits for the gather's event.
+// This is the reference scheduler's idea (run one request's communication under other requests' computation,
+// src/schedule.h:221-278) with the decomposition along the batch instead of the output features, and with
+// communication that needs no SM, since on this GPU a persistent GEMM leaves no room for a second kernel.
+static int forward_pipelined(liger_model* m, const void* input, void* output, int batch, int seq_len, int slot0, int mb,
+                             void* stream) {
+  cudaStream_t caller = (cudaStream_t)stream;
+  Bert_Model& b = *m->model;
+  if (!m->pipe_compute) {
+    int least = 0, greatest = 0;
+    LIGER_CUDA_TRY(cudaDeviceGetStreamPriorityRange(&least, &greatest));
+    LIGER_CUDA_TRY(cudaStreamCreateWithPriority(&m->pipe_compute, cudaStreamNonBlocking, least));
+    LIGER_CUDA_TRY(cudaStreamCreateWithPriority(&m->pipe_comm, cudaStreamNonBlocking, greatest));
+    LIGER_CUDA_TRY(cudaEventCreateWithFlags(&m->ev_pipe_fork, cudaEventDisableTiming));
+    LIGER_CUDA_TRY(cudaEventCreateWithFlags(&m->ev_pipe_join, cudaEventDisableTiming));
+  }
+  while ((int)m->ev_reduced.size() < mb) {
+    cudaEvent_t e = nullptr;
+    LIGER_CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    m->ev_reduced.push_back(e);
+    LIGER_CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    m->ev_gather.push_back(e);
+  }
+  cudaStream_t s0 = m->pipe_compute, s1 = m->pipe_comm;
+  const int nslots = (int)b.slots.size();
+  const int sub = batch / mb;
+  const size_t rows = (size_t)sub * seq_len, H = b.H;
+  std::vector<std::vector<FuncWrap>> vecs;
+  for (int i = 0; i < mb; ++i)
+    vecs.push_back(b.forward((const half_t*)input + i * rows * H, (half_t*)output + i * rows * H, sub, seq_len, slot0 + i));
+  LIGER_CUDA_TRY(cudaEventRecord(m->ev_pipe_fork, caller));
+  LIGER_CUDA_TRY(cudaStreamWaitEvent(s0, m->ev_pipe_fork, 0));
+  // optional per-kernel timing: events on the stream the work is queued on
+  auto begin_rec = [&](cudaStream_t s) -> cudaEvent_t {
+    if (!m->timing) return nullptr;
+    cudaEvent_t e = m->get_event();
+    cudaEventRecord(e, s);
+    return e;
+  };
+  auto end_rec = [&](int name, cudaEvent_t e0, cudaStream_t s) {
+    if (!m->timing) return;
+    cudaEvent_t e1 = m->get_event();
+    cudaEventRecord(e1, s);
+    m->ev_rec.push_back({name, {e0, e1}});
+  };
+  std::vector<size_t> cur(mb, 0);
+  std::vector<char> pending(mb, 0);
+  DynamicNvInitParam dp;
+  dp.stream = s0;
+  int n = 0;
+  bool more = true;
+  while (more) {
+    more = false;
+    for (int i = 0; i < mb; ++i) {
+      std::vector<FuncWrap>& v = vecs[i];
+      if (cur[i] >= v.size()) continue;
+      dp.index = i;
+      if (pending[i]) {  // this micro-request's previous all-gather must have landed on every rank
+        cudaEvent_t e0 = begin_rec(s0);
+        LIGER_CUDA_TRY(cudaStreamWaitEvent(s0, m->ev_gather[i], 0));
+        end_rec(kWaitRecord, e0, s0);
+        pending[i] = 0;
+      }
+      while (cur[i] < v.size() && v[cur[i]].type != COMMUNICATION) {
+        cudaEvent_t e0 = begin_rec(s0);
+        const int rc = v[cur[i]].callback(dp);
+        end_rec(v[cur[i]].name, e0, s0);
+        if (rc != LIGER_OK) return rc;
+        ++cur[i];
+        ++n;
+      }
+      if (cur[i] < v.size()) {
+        const FuncWrap& f = v[cur[i]];
+        const COMM_ARGS& c = f.args_comm_tuple;
+        if (c.comm != nullptr && c.one_shot == 3 && !c.copy_engine) {
+          cudaEvent_t e0 = begin_rec(s0);
+          int rc = liger_allreduce_fused(c.comm, c.channel, c.partial_off, c.out_off, c.residual_in, c.hidden, c.bias, c.gamma,
+                                         c.beta, c.m, c.n, c.row_begin, c.row_end, 5, s0);
+          end_rec(f.name, e0, s0);
+          if (rc != LIGER_OK) return rc;
+          LIGER_CUDA_TRY(cudaEventRecord(m->ev_reduced[i], s0));
+          LIGER_CUDA_TRY(cudaStreamWaitEvent(s1, m->ev_reduced[i], 0));
+          e0 = begin_rec(s1);
+          rc = liger_allgather_ce(c.comm, nslots + c.channel, c.out_off, c.m, c.n, c.row_begin, c.row_end, s1);
+          end_rec(kGatherRecord, e0, s1);
+          if (rc != LIGER_OK) return rc;
+          LIGER_CUDA_TRY(cudaEventRecord(m->ev_gather[i], s1));
+          pending[i] = 1;
+          n += 2;
+        } else {  // latency-bound sizes: the one-shot collective, in line
+          cudaEvent_t e0 = begin_rec(s0);
+          const int rc = f.callback(dp);
+          end_rec(f.name, e0, s0);
+          if (rc != LIGER_OK) return rc;
+          ++n;
+        }
+        ++cur[i];
+      }
+      if (cur[i] < v.size()) more = true;
+    }
+  }
+  for (int i = 0; i < mb; ++i)
+    if (pending[i]) LIGER_CUDA_TRY(cudaStreamWaitEvent(s0, m->ev_gather[i], 0));
+  LIGER_CUDA_TRY(cudaEventRecord(m->ev_pipe_join, s0));
+  LIGER_CUDA_TRY(cudaStreamWaitEvent(caller, m->ev_pipe_join, 0));
+  return n;
+}
+
 extern "C" int liger_model_forward(liger_model* m, const void* input, void* output, int batch, int seq_len, int slot,
                                    void* stream) {
   if (!m || !input || !output) return liger::set_error(LIGER_ERR_INVALID, "model_forward: null argument");
   try {
     const int mb = m->micro_batches;
-    if (mb > 1 && m->sp.world_size > 1 && !m->timing && batch % mb == 0) {
-      Bert_Model& b = *m->model;
-      if (slot < 0) { slot = b.next_slot; b.next_slot = (b.next_slot + mb) % (int)b.slots.size(); }
-      if (slot + mb > (int)b.slots.size())
-        return liger::set_error(LIGER_ERR_INVALID, "model_forward: %d micro-batches from slot %d need %d workspace slots", mb,
-                                slot, slot + mb);
-      return forward_interleaved(m, input, output, batch, seq_len, slot, mb, stream);
+    Bert_Model& b = *m->model;
+    if (mb > 1 && m->sp.world_size > 1 && batch % mb == 0) {
+      const bool pipelined = m->overlap == 1 && liger_comm_channels(m->sp.comm) >= 2 * (int)b.slots.size();
+      if (pipelined || !m->timing) {
+        if ((slot = pick_slots(b, slot, mb, "model_forward")) < 0) return slot;
+        return pipelined ? forward_pipelined(m, input, output, batch, seq_len, slot, mb, stream)
+                         : forward_interleaved(m, input, output, batch, seq_len, slot, mb, stream);
+      }
     }
+    if ((slot = pick_slots(b, slot, 1, "model_forward")) < 0) return slot;
     return forward_sequential(m, input, output, batch, seq_len, slot, stream);
   } catch (const std::exception& e) {
     return liger::set_error(LIGER_ERR_INVALID, "model_forward: %s", e.what());
@@ -318,7 +478,22 @@ extern "C" int liger_model_set_output_sharding(liger_model* m, int sharded) {
 
 extern "C" int liger_model_set_micro_batches(liger_model* m, int micro_batches) {
   if (!m || micro_batches < 1 || micro_batches > 8) return liger::set_error(LIGER_ERR_INVALID, "model_set_micro_batches: 1..8");
+  if (micro_batches > (int)m->model->slots.size())
+    return liger::set_error(LIGER_ERR_INVALID, "model_set_micro_batches: %d micro-batches need %d workspace slots, the model has %zu",
+                            micro_batches, micro_batches, m->model->slots.size());
   m->micro_batches = micro_batches;
+  return LIGER_OK;
+}
+
+extern "C" int liger_model_set_overlap(liger_model* m, int mode) {
+  if (!m || mode < 0 || mode > 1) return liger::set_error(LIGER_ERR_INVALID, "model_set_overlap: 0 or 1");
+  m->overlap = mode;
+  return LIGER_OK;
+}
+
+extern "C" int liger_model_overlap_times(liger_model* m, double out[4]) {
+  if (!m || !out) return liger::set_error(LIGER_ERR_INVALID, "model_overlap_times: null argument");
+  for (int i = 0; i < 4; ++i) { out[i] = m->overlap_acc[i]; m->overlap_acc[i] = 0.0; }
   return LIGER_OK;
 }
 
@@ -415,8 +590,9 @@ extern "C" int liger_model_forward_host(liger_model* m, const void* host_input, 
   const int M = batch * seq_len, H = b.H, ws = m->sp.world_size, rank = m->sp.world_rank;
   const size_t bytes = (size_t)M * H * 2;
   cudaStream_t s = (cudaStream_t)stream;
-  if (slot < 0) { slot = b.next_slot; b.next_slot = (b.next_slot + 1) % (int)b.slots.size(); }
-  if (slot >= (int)b.slots.size()) return liger::set_error(LIGER_ERR_INVALID, "model_forward_host: slot %d", slot);
+  // the pass below runs `need` micro-batches on consecutive slots: choose them here, once
+  const int need = (m->micro_batches > 1 && ws > 1 && batch % m->micro_batches == 0) ? m->micro_batches : 1;
+  if ((slot = pick_slots(b, slot, need, "model_forward_host")) < 0) return slot;
   if (ws == 1) {
     try {
       const int np = forward_host_pipelined(m, host_input, host_output, batch, seq_len, slot, s);
@@ -465,6 +641,8 @@ extern "C" int liger_model_kernel_times(liger_model* m, double ms[9], long long 
     LIGER_CUDA_TRY(cudaEventSynchronize(r.second.second));
     LIGER_CUDA_TRY(cudaEventElapsedTime(&t, r.second.first, r.second.second));
     if (r.first >= 0 && r.first < 9) { ms[r.first] += t; launches[r.first] += 1; }
+    else if (r.first == kWaitRecord) { m->overlap_acc[0] += t; m->overlap_acc[1] += 1.0; }
+    else if (r.first == kGatherRecord) { m->overlap_acc[2] += t; m->overlap_acc[3] += 1.0; }
     m->ev_pool.push_back(r.second.first);
     m->ev_pool.push_back(r.second.second);
   }

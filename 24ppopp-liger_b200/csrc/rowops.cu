@@ -256,6 +256,7 @@ extern "C" int liger_add_bias_input_layernorm(const void* in, const void* gamma,
 
 extern "C" int liger_add_bias_gelu(void* x, const void* bias, int m, int n, void* stream) {
   if (!x || m <= 0 || n <= 0 || n % 8) return set_error(LIGER_ERR_INVALID, "add_bias_gelu: bad argument (n %% 8 == 0)");
+  if (((uintptr_t)x | (uintptr_t)bias) & 15u) return set_error(LIGER_ERR_INVALID, "add_bias_gelu: pointers must be 16-byte aligned");
   const DeviceInfo* d = current_device();
   if (!d) return LIGER_ERR_CUDA;
   const size_t total = (size_t)m * n / 8;
@@ -270,6 +271,9 @@ extern "C" int liger_add_qkv_bias_transpose(void* q_out, void* k_out, void* v_ou
   if (!q_out || !k_out || !v_out || !q || !k || !v || batch <= 0 || seq_len <= 0 || heads <= 0 || head_dim <= 0 ||
       head_dim % 8)
     return set_error(LIGER_ERR_INVALID, "add_qkv_bias_transpose: bad argument (head_dim %% 8 == 0)");
+  if (((uintptr_t)q_out | (uintptr_t)k_out | (uintptr_t)v_out | (uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)bq |
+       (uintptr_t)bk | (uintptr_t)bv) & 15u)
+    return set_error(LIGER_ERR_INVALID, "add_qkv_bias_transpose: pointers must be 16-byte aligned");
   const DeviceInfo* d = current_device();
   if (!d) return LIGER_ERR_CUDA;
   const size_t total = (size_t)3 * batch * seq_len * heads * (head_dim / 8);
@@ -283,6 +287,7 @@ extern "C" int liger_transpose_heads(void* dst, const void* src, int batch, int 
                                      void* stream) {
   if (!dst || !src || batch <= 0 || seq_len <= 0 || heads <= 0 || head_dim <= 0 || head_dim % 8)
     return set_error(LIGER_ERR_INVALID, "transpose_heads: bad argument (head_dim %% 8 == 0)");
+  if (((uintptr_t)dst | (uintptr_t)src) & 15u) return set_error(LIGER_ERR_INVALID, "transpose_heads: pointers must be 16-byte aligned");
   const DeviceInfo* d = current_device();
   if (!d) return LIGER_ERR_CUDA;
   const size_t total = (size_t)batch * seq_len * heads * (head_dim / 8);

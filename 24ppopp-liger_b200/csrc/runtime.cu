@@ -5,7 +5,9 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <cstdlib>
 #include <mutex>
+#include <vector>
 
 namespace liger {
 
@@ -22,6 +24,24 @@ int set_error(int code, const char* fmt, ...) {
 static const int kMaxDevices = 64;
 static DeviceInfo g_dev[kMaxDevices];
 static std::mutex g_dev_mu;
+
+static std::vector<WaitBudgetSetter>& wait_budget_setters() {
+  static std::vector<WaitBudgetSetter> v;
+  return v;
+}
+void register_wait_budget_setter(WaitBudgetSetter fn) { wait_budget_setters().push_back(fn); }
+static unsigned long long g_wait_budget_ms[kMaxDevices];  // 0 = the built-in default
+
+// Sets the budget of every translation unit's copy on the current device.
+static int apply_wait_budget(int dev, unsigned long long ms) {
+  const unsigned long long ns = ms * 1000000ull;
+  for (WaitBudgetSetter fn : wait_budget_setters()) {
+    cudaError_t e = fn(ns);
+    if (e != cudaSuccess) return set_error(LIGER_ERR_CUDA, "setting the wait budget failed: %s", cudaGetErrorString(e));
+  }
+  g_wait_budget_ms[dev] = ms;
+  return LIGER_OK;
+}
 
 const DeviceInfo* current_device() {
   int dev = -1;
@@ -58,6 +78,11 @@ const DeviceInfo* current_device() {
   d.status_host = (DeviceStatus*)h;
   d.status_dev = (DeviceStatus*)dptr;
   d.device = dev;
+  // LIGER_WAIT_BUDGET_MS: budget of the bounded device-side waits on every device this process uses
+  if (const char* env = getenv("LIGER_WAIT_BUDGET_MS")) {
+    const long ms = atol(env);
+    if (ms > 0 && apply_wait_budget(dev, (unsigned long long)ms) != LIGER_OK) return nullptr;
+  }
   return &d;
 }
 
@@ -150,6 +175,15 @@ int liger_device_status(unsigned int out[4]) {
   unsigned int code = s->code;
   if (out) { out[0] = code; out[1] = s->where; out[2] = s->detail0; out[3] = s->detail1; }
   return (int)code;
+}
+
+int liger_set_wait_budget_ms(int milliseconds) {
+  if (milliseconds < 1 || milliseconds > 600000)
+    return liger::set_error(LIGER_ERR_INVALID, "set_wait_budget_ms: 1 .. 600000 ms");
+  const liger::DeviceInfo* d = liger::current_device();
+  if (!d) return LIGER_ERR_CUDA;
+  std::lock_guard<std::mutex> lk(liger::g_dev_mu);
+  return liger::apply_wait_budget(d->device, (unsigned long long)milliseconds);
 }
 
 int liger_device_status_clear(void) {

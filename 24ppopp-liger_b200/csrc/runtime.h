@@ -45,4 +45,18 @@ int make_tmap_3d_f16(CUtensorMap* map, const void* base, uint64_t inner, uint64_
 // Launch-error check after a <<<>>> launch.
 int check_launch(const char* what);
 
+// Every translation unit whose kernels make bounded waits owns a copy of g_wait_budget_ns (common.cuh) and
+// registers a function that sets it on the current device.
+typedef cudaError_t (*WaitBudgetSetter)(unsigned long long ns);
+void register_wait_budget_setter(WaitBudgetSetter fn);
+#define LIGER_REGISTER_WAIT_BUDGET()                                                                  \
+  namespace {                                                                                         \
+  cudaError_t liger_tu_set_wait_budget(unsigned long long ns) {                                       \
+    return cudaMemcpyToSymbol(::liger::g_wait_budget_ns, &ns, sizeof(ns));                            \
+  }                                                                                                   \
+  struct LigerTuWaitBudgetRegistration {                                                              \
+    LigerTuWaitBudgetRegistration() { ::liger::register_wait_budget_setter(&liger_tu_set_wait_budget); } \
+  } liger_tu_wait_budget_registration;                                                                \
+  }
+
 }  // namespace liger

@@ -48,10 +48,18 @@ inline void host_check(int rc, const char* what) {
 inline void cuda_check(cudaError_t e, const char* what) {
   if (e != cudaSuccess) throw std::runtime_error(std::string(what) + ": " + cudaGetErrorString(e));
 }
+// While a Bert_Model is under construction on this thread, every device allocation its layers make is
+// recorded here, so that the model can free them when it is destroyed (the reference's layers never free
+// anything: src/layer/linear.h:40, src/layer/bert_layer.h:115-118).
+inline std::vector<void*>*& alloc_sink() {
+  static thread_local std::vector<void*>* sink = nullptr;
+  return sink;
+}
 template <typename T>
 inline T* device_alloc(size_t count, const char* what) {
   void* p = nullptr;
   cuda_check(cudaMalloc(&p, count * sizeof(T) > 0 ? count * sizeof(T) : 16), what);
+  if (alloc_sink()) alloc_sink()->push_back(p);
   return (T*)p;
 }
 inline size_t round_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -202,6 +210,9 @@ class Bert_MHA {
     qkv_bias = device_alloc<half_t>(3 * Hl, "qkv_bias");
     w_bias = device_alloc<half_t>(n, "w_bias");
   }
+  ~Bert_MHA() { delete linear_qkv_col; delete linear_w_row; }
+  Bert_MHA(const Bert_MHA&) = delete;
+  Bert_MHA& operator=(const Bert_MHA&) = delete;
 
   std::vector<FuncWrap> forward(const void* input, Workspace& w, const PostOp& post, const Shape& sh) const {
     std::vector<FuncWrap> vec;
@@ -325,6 +336,9 @@ class Bert_MLP {
     bias = device_alloc<half_t>(up_cols_local, "ffn bias");
     down_bias = device_alloc<half_t>(n, "ffn down bias");
   }
+  ~Bert_MLP() { delete linear_col; delete linear_row; }
+  Bert_MLP(const Bert_MLP&) = delete;
+  Bert_MLP& operator=(const Bert_MLP&) = delete;
 
   // has_post = false only for the last layer of the pre-LN graph with world_size == 1 (nothing follows)
   std::vector<FuncWrap> forward(const void* input, Workspace& w, const PostOp& post, const Shape& sh) const {
@@ -366,6 +380,9 @@ class Bert_Encoder {
     ln_mha = new LayerNorm(k);
     ln_mlp = new LayerNorm(k);
   }
+  ~Bert_Encoder() { delete MHA; delete MLP; delete ln_mha; delete ln_mlp; }
+  Bert_Encoder(const Bert_Encoder&) = delete;
+  Bert_Encoder& operator=(const Bert_Encoder&) = delete;
   // concatenation of the two blocks' kernel vectors (src/layer/bert.h:59-79)
   std::vector<FuncWrap> forward(const void* mha_in, const PostOp& mha_post, const void* mlp_in, const PostOp& mlp_post,
                                 Workspace& w, const Shape& sh) const {
@@ -386,8 +403,23 @@ class Bert_Model {
   std::vector<Bert_Encoder*> encoders;
   std::vector<Workspace> slots;
   int next_slot = 0;
+  std::vector<void*> allocations;  // every cudaMalloc made for this model; freed by the destructor
+
+  // Unlike the reference's model (no destructors anywhere), this one owns its device memory: destroying it
+  // frees weights, caches and workspaces.  Closures returned by forward() must not outlive it.
+  ~Bert_Model() {
+    for (auto* e : encoders) delete e;
+    for (void* p : allocations) cudaFree(p);
+  }
+  Bert_Model(const Bert_Model&) = delete;
+  Bert_Model& operator=(const Bert_Model&) = delete;
 
   Bert_Model(const BertInitParam& bp, const StaticNvInitParam& sp) : BertParams(bp), SParam(sp) {
+    struct SinkGuard {
+      std::vector<void*>* prev;
+      explicit SinkGuard(std::vector<void*>* mine) : prev(alloc_sink()) { alloc_sink() = mine; }
+      ~SinkGuard() { alloc_sink() = prev; }
+    } guard(&allocations);
     const int ws = sp.world_size;
     H = bp.hidden(); F = bp.ffn(); D = bp.size_per_head; k = n = H;
     if (ws < 1 || bp.head_num % ws || F % ws || H % 8 || D % 8)

@@ -54,6 +54,13 @@ LIGER_API const char* liger_version(void);
  */
 LIGER_API int liger_device_status(unsigned int out[4]);
 LIGER_API int liger_device_status_clear(void);
+/*
+ * How long a kernel of this library waits (on an mbarrier, a peer's flag, a barrier across ranks) before it
+ * gives up, sets LIGER_DEV_TIMEOUT and unwinds: 2000 ms unless set here (for the current device) or through the
+ * environment variable LIGER_WAIT_BUDGET_MS (every device).  The reference has no counterpart: its kernels
+ * and NCCL's wait without limit (src/layer/func_wrapper.h:40-43).
+ */
+LIGER_API int liger_set_wait_budget_ms(int milliseconds);
 
 /* ------------------------------------------------------------------------------------------ */
 /* Seeded tensors (the reference leaves every buffer uninitialised: src/layer/linear.h:40,92,  */
@@ -261,6 +268,7 @@ LIGER_API void* liger_comm_data(liger_comm* comm);
 LIGER_API size_t liger_comm_data_bytes(liger_comm* comm);
 LIGER_API int liger_comm_rank(liger_comm* comm);
 LIGER_API int liger_comm_world_size(liger_comm* comm);
+LIGER_API int liger_comm_channels(liger_comm* comm);
 
 /*
  * Where the fused all-reduce launches of `channel` spent their time since the last reset, summed over
@@ -290,6 +298,8 @@ LIGER_API int liger_comm_timing(liger_comm* comm, int channel, int reset, double
  * owners by GEMMs with LIGER_EPI_SCATTER (partial_off is then the [world_size][rows][N] receive
  * region) and the reduction reads local memory only.  one_shot == 2 turns the call into an all-gather: each rank's own rows of its
  * partial are taken as they are (no sum over peers) and stored to every rank.
+ * one_shot == 5: input as for 3, but the finished rows are stored into this rank's own segment only and there is no
+ * exit barrier -- the first half of a split collective whose second half is liger_allgather_ce on another stream.
  * Waits on peers are bounded; on timeout the device status word is set.
  * N % 8 == 0, N <= 16384.  row_begin / row_end allow the collective to be issued in slices
  * (decompose_comm_callback, src/utils.h:262-281).
@@ -312,6 +322,17 @@ LIGER_API int liger_allreduce_fused(liger_comm* comm, int channel, size_t partia
 LIGER_API int liger_allreduce_ce(liger_comm* comm, int channel, size_t partial_off, size_t recv_off, size_t out_off,
                                  const void* residual_in, void* hidden, const void* bias, const void* gamma,
                                  const void* beta, int m, int n, int row_begin, int row_end, void* stream);
+
+/*
+ * All-gather by the copy engines, the second half of a split all-reduce (the reference's unused Allgather
+ * wrapper, src/layer/func_wrapper.h:50-53, is the nearest counterpart): rows [row_begin, row_end) that this
+ * rank owns (rank r owns rows [r*ceil(m/ws), (r+1)*ceil(m/ws)) of the [m, n] tensor at out_off) are copied to
+ * the same place in every peer's segment with one peer copy per peer, followed by a one-warp barrier kernel on
+ * `channel`, after which every rank holds all rows.  No SM moves data, so the transfer runs underneath the
+ * kernels of another stream.  Use a channel of its own when other collectives are in flight on other streams.
+ */
+LIGER_API int liger_allgather_ce(liger_comm* comm, int channel, size_t out_off, int m, int n, int row_begin, int row_end,
+                                 void* stream);
 
 /* ------------------------------------------------------------------------------------------ */
 /* The layer stack and the serving entry points                                               */
@@ -392,6 +413,27 @@ LIGER_API int liger_model_fill_kv_cache(liger_model* model);
  * Results are identical to the un-split pass (rows are independent across sequences).
  */
 LIGER_API int liger_model_set_micro_batches(liger_model* model, int micro_batches);
+/*
+ * How the micro-requests of liger_model_set_micro_batches share the GPU.
+ *   1 (default): one compute stream runs the compute segments of all micro-requests in turn; every all-reduce is
+ *      split into the reduce-scatter done by the row-parallel GEMM's epilogue, a short local reduction
+ *      (+ residual + LayerNorm) on the compute stream, and an all-gather by the copy engines on a second stream
+ *      (liger_allgather_ce) that runs underneath the other micro-request's next compute segment.  Needs a
+ *      communicator with at least 2 * workspace_slots channels; with fewer, mode 0 is used.
+ *   0: one stream per micro-request, all-reduces entirely in kernels (liger_allreduce_fused).
+ * Both give the bits of the un-split pass.  This is the reference's decomposition + two-stream interleaving
+ * (src/init.h:226-259, src/schedule.h:221-278) re-derived for a GPU whose persistent GEMMs leave no SM resources
+ * for a concurrent communication kernel: the decomposition is along the batch, and the overlapped half of the
+ * communication uses no SM.
+ */
+LIGER_API int liger_model_set_overlap(liger_model* model, int mode);
+/*
+ * After liger_model_kernel_times() on passes run with mode 1: out[0] = milliseconds the compute stream spent
+ * blocked waiting for an all-gather (exposed communication beyond the local reductions, which are counted under
+ * kernel names 3 and 6), out[1] = number of such waits, out[2] = milliseconds of the copy-engine all-gathers on the
+ * communication stream, out[3] = their number.  Clears the sums.
+ */
+LIGER_API int liger_model_overlap_times(liger_model* model, double out[4]);
 
 /* world_size > 1, liger_model_forward_host only.  sharded = 1: every rank copies rows
  * [rank * ceil(M / world_size), ...) of the result -- the rows it uploaded -- to the same offsets of ITS

@@ -126,6 +126,15 @@ def attention(q, k, v, mask=None, causal=False, scale=None):
     return out
 
 
+def masked_softmax(scores, mask, scale):
+    """softmax(scale * scores + (1 - mask) * -10000) over the last axis; scores [B,h,S,S], mask [B,S,S] or None."""
+    s = _f32(scores).copy()
+    B, h, S, _ = s.shape
+    m = _f32(mask) if mask is not None else None
+    lib().lo_masked_softmax(_p(s), _p(m), B, h, S, C.c_float(scale))
+    return s
+
+
 def add_bias_gelu(x, bias):
     x = _f32(x).copy()
     b = _f32(bias) if bias is not None else None

@@ -243,6 +243,28 @@ LO_API void lo_attention(const float* q, const float* k, const float* v, const f
     }
 }
 
+/* The masked softmax alone, in place on scores [B,h,S,S]: src/cuda/attention_kernels.cu:543-573,620-680
+ * (attn_softmax_kernelLauncher): p = exp(t - max t) / (sum + 1e-6), t = scale*s + (1-mask)*(-10000),
+ * mask [B,S,S] of 0/1 shared over heads.  The same arithmetic as inside lo_attention. */
+LO_API void lo_masked_softmax(float* scores, const float* mask, int B, int h, int S, float scale) {
+#pragma omp parallel for collapse(2) schedule(static)
+  for (int b = 0; b < B; ++b)
+    for (int hh = 0; hh < h; ++hh)
+      for (int i = 0; i < S; ++i) {
+        float* t = scores + (((size_t)b * h + hh) * S + i) * S;
+        float mx = -1e20f;
+        for (int j = 0; j < S; ++j) {
+          const float m = mask ? mask[((size_t)b * S + i) * S + j] : 1.0f;
+          t[j] = scale * t[j] + (1.0f - m) * -10000.0f;
+          if (t[j] > mx) mx = t[j];
+        }
+        float sum = 0.0f;
+        for (int j = 0; j < S; ++j) { t[j] = expf(t[j] - mx); sum += t[j]; }
+        const float inv = 1.0f / (sum + 1e-6f);
+        for (int j = 0; j < S; ++j) t[j] *= inv;
+      }
+}
+
 /* ------------------------------------------------------------------------------------------ */
 /* bias + GELU (tanh form): src/cuda/cuda_kernels.cu:9-29,71-84                                */
 /* ------------------------------------------------------------------------------------------ */

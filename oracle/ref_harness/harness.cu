@@ -9,6 +9,12 @@
 // repository's kernels are linked into it.
 //
 //   liger_ref_harness <batch> <seq> <head_num> <size_per_head> <layers> <steps> <warmup> [dump_file]
+//   liger_ref_harness ops <dump_dir>
+//
+// The second form runs the reference's own kernels and its cuBLAS-backed linear layers one at a time
+// on seeded inputs (tensor ids 0x20000 + ...) and writes each result as raw fp16 to
+// <dump_dir>/<name>.f16, with a manifest of names and shapes on stdout: the per-operator vectors
+// that pin the CPU oracle and this repository's kernels to the reference's own output.
 //
 // Rank / world size come from the MPI stand-in's environment (RANK / WORLD_SIZE under torchrun).
 // The reference's workspace slot for the attention scores is max_batch*max_seq*H/ws elements although
@@ -75,9 +81,153 @@ static void fw(__half* dst, int rows, int cols, int row0, int col0, int ld, uint
   fill_window<<<1184, 256>>>(dst, rows, cols, row0, col0, ld, 0u, id, mean, std);
 }
 
+// ---- per-operator vectors -----------------------------------------------------------------------------
+static __half* dalloc(size_t n) {
+  __half* p = nullptr;
+  if (cudaMalloc((void**)&p, sizeof(__half) * (n ? n : 1)) != cudaSuccess) { fprintf(stderr, "cudaMalloc failed\n"); exit(3); }
+  return p;
+}
+static __half* seeded(size_t rows, size_t cols, uint32_t id, float mean, float std) {
+  __half* p = dalloc(rows * cols);
+  fw(p, (int)rows, (int)cols, 0, 0, (int)cols, id, mean, std);
+  return p;
+}
+static std::string g_dir;
+static std::string g_manifest;
+static void dump(const char* name, const __half* dev, std::initializer_list<int> shape) {
+  size_t n = 1;
+  for (int s : shape) n *= (size_t)s;
+  std::vector<__half> h(n);
+  if (cudaMemcpy(h.data(), dev, n * sizeof(__half), cudaMemcpyDeviceToHost) != cudaSuccess) {
+    fprintf(stderr, "ops: copy of %s failed: %s\n", name, cudaGetErrorString(cudaGetLastError()));
+    exit(4);
+  }
+  const std::string path = g_dir + "/" + name + ".f16";
+  FILE* f = fopen(path.c_str(), "wb");
+  if (!f || fwrite(h.data(), sizeof(__half), n, f) != n) { fprintf(stderr, "ops: cannot write %s\n", path.c_str()); exit(5); }
+  fclose(f);
+  if (!g_manifest.empty()) g_manifest += ", ";
+  g_manifest += std::string("\"") + name + "\": [";
+  bool first = true;
+  for (int s : shape) { g_manifest += (first ? "" : ", ") + std::to_string(s); first = false; }
+  g_manifest += "]";
+}
+// mask[b][q][k]: batch 0 causal (k <= q), other batches padding (the last quarter of the keys masked out)
+__global__ void fill_mask(__half* mask, int B, int S) {
+  const size_t total = (size_t)B * S * S;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int k = (int)(i % S), q = (int)((i / S) % S), b = (int)(i / ((size_t)S * S));
+    const bool keep = b == 0 ? k <= q : k < S - S / 4;
+    mask[i] = __float2half(keep ? 1.0f : 0.0f);
+  }
+}
+
+static int run_ops(const char* dir, const StaticNvInitParam& SParams) {
+  g_dir = dir;
+  DynamicNvInitParam DParams;
+  cudaStream_t st = DParams.stream;
+  {  // LayerNorm (src/cuda/cuda_kernels.cu:463-532), two widths
+    const int shapes[2][2] = {{24, 1024}, {8, 12288}};
+    for (int c = 0; c < 2; ++c) {
+      const int m = shapes[c][0], n = shapes[c][1];
+      const uint32_t id = 0x20000u + 8u * c;
+      __half *x = seeded(m, n, id, 0.3f, 1.5f), *g = seeded(1, n, id + 1, 1.0f, 0.02f), *b = seeded(1, n, id + 2, 0.0f, 0.02f);
+      __half* y = dalloc((size_t)m * n);
+      layer_norm<__half>(x, g, b, y, m, n, st);
+      cudaStreamSynchronize(st);
+      dump(c == 0 ? "layernorm_1024" : "layernorm_12288", y, {m, n});
+    }
+  }
+  {  // bias + GELU in place (src/cuda/cuda_kernels.cu:71-84,302-319)
+    const int m = 40, n = 4096;
+    __half *x = seeded(m, n, 0x20010u, 0.0f, 1.5f), *b = seeded(1, n, 0x20011u, 0.0f, 0.5f);
+    add_bias_act_kernelLauncher<__half>(x, b, m, n, st);
+    cudaStreamSynchronize(st);
+    dump("bias_gelu", x, {m, n});
+  }
+  {  // bias + head split (src/cuda/attention_kernels.cu:133-163,226-329): k <= 1024 and k > 1024 launch paths
+    const int cases[2][4] = {{2, 64, 4, 64}, {2, 64, 16, 128}};
+    for (int c = 0; c < 2; ++c) {
+      const int B = cases[c][0], S = cases[c][1], h = cases[c][2], D = cases[c][3], k = h * D, m = B * S;
+      const uint32_t id = 0x20020u + 8u * c;
+      __half *Q = seeded(m, k, id, 0.0f, 1.0f), *K = seeded(m, k, id + 1, 0.0f, 1.0f), *V = seeded(m, k, id + 2, 0.0f, 1.0f);
+      __half *bq = seeded(1, k, id + 3, 0.0f, 0.5f), *bk = seeded(1, k, id + 4, 0.0f, 0.5f), *bv = seeded(1, k, id + 5, 0.0f, 0.5f);
+      __half *qo = dalloc((size_t)m * k), *ko = dalloc((size_t)m * k), *vo = dalloc((size_t)m * k);
+      add_QKV_bias_transpose_kernelLauncher<__half>(qo, ko, vo, Q, bq, K, bk, V, bv, B, S, h, D, st);
+      cudaStreamSynchronize(st);
+      const std::string tag = c == 0 ? "qkv_split_256" : "qkv_split_2048";
+      dump((tag + "_q").c_str(), qo, {B, h, S, D});
+      dump((tag + "_k").c_str(), ko, {B, h, S, D});
+      dump((tag + "_v").c_str(), vo, {B, h, S, D});
+    }
+  }
+  {  // scaled masked softmax in place (src/cuda/attention_kernels.cu:543-573,620-680)
+    const int cases[2][3] = {{2, 4, 64}, {2, 2, 200}};
+    for (int c = 0; c < 2; ++c) {
+      const int B = cases[c][0], h = cases[c][1], S = cases[c][2];
+      __half* s = seeded((size_t)B * h * S, S, 0x20030u + (uint32_t)c, 0.0f, 8.0f);
+      __half* mask = dalloc((size_t)B * S * S);
+      fill_mask<<<64, 256, 0, st>>>(mask, B, S);
+      attn_softmax_kernelLauncher<__half>(s, mask, B, S, h, __float2half(0.125f), st);
+      cudaStreamSynchronize(st);
+      dump(c == 0 ? "softmax_64" : "softmax_200", s, {B, h, S, S});
+    }
+  }
+  {  // head merge (src/cuda/attention_kernels.cu:693-742)
+    const int B = 2, h = 4, S = 64, D = 64;
+    __half* src = seeded((size_t)B * h * S, D, 0x20040u, 0.0f, 1.0f);
+    __half* dst = dalloc((size_t)B * S * h * D);
+    transpose_kernelLauncher<__half>(dst, src, B, S, h, D, st);
+    cudaStreamSynchronize(st);
+    dump("merge_heads", dst, {B * S, h * D});
+  }
+  {  // residual + bias + LayerNorm (src/cuda/cuda_kernels.cu:360-409) and residual + bias (:438-461)
+    const int m = 24, n = 1024;
+    __half *in = seeded(m, n, 0x20050u, 0.0f, 1.0f), *g = seeded(1, n, 0x20051u, 1.0f, 0.02f), *b = seeded(1, n, 0x20052u, 0.0f, 0.02f);
+    __half *bias = seeded(1, n, 0x20053u, 0.0f, 0.5f), *out = seeded(m, n, 0x20054u, 0.0f, 1.0f), *norm = dalloc((size_t)m * n);
+    add_bias_input_layernorm_2_kernelLauncher<__half>(in, g, b, bias, out, norm, m, n, st);
+    cudaStreamSynchronize(st);
+    dump("residual_ln_hidden", out, {m, n});
+    dump("residual_ln_norm", norm, {m, n});
+    __half *o2 = seeded(m, n, 0x20060u, 0.0f, 1.0f), *i2 = seeded(m, n, 0x20061u, 0.0f, 1.0f), *b2 = seeded(1, n, 0x20062u, 0.0f, 0.5f);
+    add_bias_input_kernelLauncher<__half>(o2, b2, i2, m, n, st);
+    cudaStreamSynchronize(st);
+    dump("residual_add", o2, {m, n});
+  }
+  {  // the reference's linear layers = cublasGemmEx as bound in src/layer/linear.h:47-53,99-105
+    const int m1 = 96, k1 = 1024, n1 = 512;
+    Linear_Col<__half> col(SParams, k1, n1);
+    fw(col.weights, k1, n1, 0, 0, n1, 0x20071u, 0.0f, 0.02f);
+    __half *x1 = seeded(m1, k1, 0x20070u, 0.0f, 1.0f), *y1 = dalloc((size_t)m1 * n1);
+    for (auto& f : col.forward(x1, y1, m1)) f.callback(DParams);
+    cudaStreamSynchronize(st);
+    dump("linear_col", y1, {m1, n1});
+    const int m2 = 64, k2 = 4096, n2 = 1024;
+    Linear_Row<__half> row(SParams, k2, n2);
+    fw(row.weights, k2, n2, 0, 0, n2, 0x20073u, 0.0f, 0.02f);
+    __half *x2 = seeded(m2, k2, 0x20072u, 0.0f, 1.0f), *y2 = dalloc((size_t)m2 * n2);
+    for (auto& f : row.forward(x2, y2, m2)) f.callback(DParams);
+    cudaStreamSynchronize(st);
+    dump("linear_row", y2, {m2, n2});
+  }
+  const cudaError_t err = cudaDeviceSynchronize();
+  printf("{\"ref_ops\": true, \"cuda_error\": \"%s\", \"tensors\": {%s}}\n", cudaGetErrorString(err), g_manifest.c_str());
+  fflush(stdout);
+  return err == cudaSuccess ? 0 : 4;
+}
+
 int main(int argc, char* argv[]) {
+  if (argc == 3 && std::string(argv[1]) == "ops") {
+    int ws = 1, wr = 0;
+    ncclComm_t nc = createNcclComm(argc, argv, ws, wr);
+    StaticNvInitParam SP(wr, ws, nc, 1);
+    const int rc = ws == 1 ? run_ops(argv[2], SP) : 2;
+    MPI_Finalize();
+    return rc;
+  }
   if (argc < 8) {
-    fprintf(stderr, "usage: %s batch seq head_num size_per_head layers steps warmup [dump_file]\n", argv[0]);
+    fprintf(stderr, "usage: %s batch seq head_num size_per_head layers steps warmup [dump_file]\n       %s ops dump_dir\n", argv[0],
+            argv[0]);
     return 2;
   }
   int batch = atoi(argv[1]), seq = atoi(argv[2]), head_num = atoi(argv[3]), size_per_head = atoi(argv[4]);
@@ -153,21 +303,19 @@ int main(int argc, char* argv[]) {
   cudaEventElapsedTime(&ms, e0, e1);
   MPI_Barrier(MPI_COMM_WORLD);
 
-  // end to end: host input -> device, the pass, result -> host, every step (every rank needs the input)
-  for (int i = 0; i < 2; ++i) {
+  // end to end: host input -> device, the pass, result -> host, every step.  Every rank needs the whole
+  // input (the reference has no way to distribute it); the result is replicated, so rank 0 alone downloads it.
+  auto step_e2e = [&]() {
     cudaMemcpyAsync(input, hin, sizeof(__half) * (size_t)M * H, cudaMemcpyHostToDevice, DParams.stream);
     step();
-    cudaMemcpyAsync(hout, output, sizeof(__half) * (size_t)M * H, cudaMemcpyDeviceToHost, DParams.stream);
+    if (world_rank == 0)
+      cudaMemcpyAsync(hout, output, sizeof(__half) * (size_t)M * H, cudaMemcpyDeviceToHost, DParams.stream);
     cudaStreamSynchronize(DParams.stream);
-  }
+  };
+  for (int i = 0; i < 2; ++i) step_e2e();
   MPI_Barrier(MPI_COMM_WORLD);
   cudaEventRecord(e0, DParams.stream);
-  for (int i = 0; i < steps; ++i) {
-    cudaMemcpyAsync(input, hin, sizeof(__half) * (size_t)M * H, cudaMemcpyHostToDevice, DParams.stream);
-    step();
-    cudaMemcpyAsync(hout, output, sizeof(__half) * (size_t)M * H, cudaMemcpyDeviceToHost, DParams.stream);
-    cudaStreamSynchronize(DParams.stream);
-  }
+  for (int i = 0; i < steps; ++i) step_e2e();
   cudaEventRecord(e1, DParams.stream);
   cudaEventSynchronize(e1);
   float ms_e2e = 0.0f;

@@ -54,3 +54,27 @@ def test_argument_validation_without_gpu(liger):
     assert lib.liger_gemm_fp16(ctypes.byref(args), None) == -1
     assert b"positive" in lib.liger_last_error()
     assert lib.liger_layernorm(None, None, None, None, 4, 64, None) == -1
+
+
+def test_misaligned_pointers_and_short_rows_are_rejected_without_gpu(liger):
+    """Entry points whose kernels use 16-byte vector accesses refuse pointers that are not 16-byte aligned, and the
+    decode entry points refuse an output row shorter than heads * head_dim, before anything is launched (the
+    pointers below are never dereferenced)."""
+    lib = liger.lib()
+    ok, odd = 0x7f0000001000, 0x7f0000001008   # 16-byte aligned / only 8-byte aligned
+    assert lib.liger_add_bias_gelu(odd, ok, 4, 64, None) == -1
+    assert b"aligned" in lib.liger_last_error()
+    assert lib.liger_add_bias_gelu(ok, odd, 4, 64, None) == -1
+    for bad in range(9):
+        ptrs = [odd if i == bad else ok for i in range(9)]
+        assert lib.liger_add_qkv_bias_transpose(*ptrs, 2, 8, 2, 64, None) == -1, bad
+        assert b"aligned" in lib.liger_last_error()
+    assert lib.liger_transpose_heads(odd, ok, 2, 8, 2, 64, None) == -1
+    assert lib.liger_transpose_heads(ok, odd, 2, 8, 2, 64, None) == -1
+    # decode: out row shorter than heads * head_dim; scratch not 4-byte aligned
+    assert lib.liger_attention_decode(ok, ok, ok, ok, ok, 2, 4, 100, 128, 64, 4 * 64 - 8, 0.125, None) == -1
+    assert b"ldo" in lib.liger_last_error()
+    assert lib.liger_attention_decode(ok, ok, ok, ok, ok + 2, 2, 4, 100, 128, 64, 4 * 64, 0.125, None) == -1
+    assert b"scratch" in lib.liger_last_error()
+    assert lib.liger_attention_decode_noalloc(ok, ok, ok, ok, 2, 4, 100, 128, 64, 4 * 64 - 8, 0.125, None) == -1
+    assert b"ldo" in lib.liger_last_error()

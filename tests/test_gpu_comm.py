@@ -96,3 +96,75 @@ def test_allreduce_fused_two_ranks(oracle):
                 assert_close(got_h[rows], want_h[rows], rel=1e-2, what=f"rank {r} {key} hidden")
         # every rank ends with the same bits
         assert np.array_equal(results[0][key][0], results[1][key][0]) or mode == "one_shot"
+
+
+def _two_ranks_in_one_process(liger, lib, data_bytes, channels=1):
+    """Both ends of a 2-rank communicator on this one GPU (handles exchanged in memory, peers mapped directly)."""
+    import ctypes as C
+    handles = [C.c_void_p(), C.c_void_p()]
+    blobs = b""
+    for r in range(2):
+        liger.check(lib.liger_comm_create(C.byref(handles[r]), r, 2, data_bytes, channels))
+        blob = (C.c_uint8 * liger.capi.COMM_HANDLE_BYTES)()
+        liger.check(lib.liger_comm_export(handles[r], blob))
+        blobs += bytes(blob)
+    for r in range(2):
+        liger.check(lib.liger_comm_connect(handles[r], blobs))
+    return handles
+
+
+def test_bounded_wait_gives_up_and_the_context_stays_usable(gpu, liger):
+    """Failure detection without a fault: rank 1 of a 2-rank communicator never launches its side of the collective,
+    so rank 0's barrier waits on a flag that nothing sets.  With the wait budget at 50 ms the kernels give up,
+    record LIGER_DEV_TIMEOUT with the entry barrier's location id, and return; after clearing the status the next
+    launch works as if nothing had happened."""
+    import ctypes as C
+    import time
+    import torch
+    from helpers import dev_fill, ptr, stream_ptr
+    lib = gpu
+    m, n = 16, 1024
+    bytes_t = m * n * 2
+    handles = _two_ranks_in_one_process(liger, lib, 2 * bytes_t)
+    st = (C.c_uint * 4)()
+    assert lib.liger_device_status(C.byref(st)) == 0
+    liger.check(lib.liger_set_wait_budget_ms(50))
+    try:
+        torch.cuda.synchronize()
+        t0 = time.time()
+        liger.check(lib.liger_allreduce_fused(handles[0], 0, 0, bytes_t, None, None, None, None, None, m, n, 0, m, 0, stream_ptr()))
+        torch.cuda.synchronize()
+        elapsed = time.time() - t0
+        assert lib.liger_device_status(C.byref(st)) == liger.capi.DEV_TIMEOUT
+        assert st[0] == liger.capi.DEV_TIMEOUT and st[1] == 0x200 and st[2] == 1, list(st)   # entry barrier, waiting for rank 1
+        assert 0.04 < elapsed < 2.0, elapsed   # two waits of 50 ms (entry and exit barrier), not the default 2 s each
+    finally:
+        liger.check(lib.liger_set_wait_budget_ms(2000))
+    liger.check(lib.liger_device_status_clear())
+    assert lib.liger_device_status(C.byref(st)) == 0
+    # the context is intact: an ordinary launch runs and is correct
+    x = dev_fill(liger, 8, 1024, 0, 900)
+    g = torch.ones(1024, dtype=torch.float16, device="cuda")
+    b = torch.zeros(1024, dtype=torch.float16, device="cuda")
+    y = torch.empty_like(x)
+    liger.check(lib.liger_layernorm(ptr(x), ptr(g), ptr(b), ptr(y), 8, 1024, stream_ptr()))
+    torch.cuda.synchronize()
+    want = torch.nn.functional.layer_norm(x.float(), (1024,), eps=1e-6)
+    assert (y.float() - want).abs().max().item() < 2e-2
+    assert lib.liger_device_status(C.byref(st)) == 0
+    for h in handles:
+        lib.liger_comm_destroy(h)
+    assert lib.liger_set_wait_budget_ms(0) == -1
+
+
+def test_copy_engine_collective_rejects_misaligned_pointers(gpu, liger):
+    import ctypes as C
+    lib = gpu
+    h = C.c_void_p()
+    liger.check(lib.liger_comm_create(C.byref(h), 0, 1, 1 << 20, 1))
+    ok, odd = 0x7f0000001000, 0x7f0000001008
+    assert lib.liger_allreduce_ce(h, 0, 0, 65536, 131072, None, odd, None, None, None, 8, 64, 0, 8, None) == -1
+    assert b"aligned" in lib.liger_last_error()
+    assert lib.liger_allreduce_ce(h, 0, 0, 65536, 131072, None, ok, odd, None, None, 8, 64, 0, 8, None) == -1
+    assert lib.liger_allgather_ce(h, 3, 0, 8, 64, 0, 8, None) == -1    # channel out of range
+    lib.liger_comm_destroy(h)

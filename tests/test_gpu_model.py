@@ -120,8 +120,10 @@ def _tp_worker(rank, world, port, case, results):
     c = CASES[case]
     H = c["head_num"] * c["size_per_head"]
     M = c["B"] * c["S"]
-    cfg = make_cfg(liger, case)
-    comm = Comm(rank, world, lib.liger_model_comm_bytes(C.byref(cfg), world), channels=cfg.workspace_slots)
+    cfg = make_cfg(liger, case, slots=4)
+    # two flag sets per workspace slot: the pipelined schedule keeps a slot's copy-engine all-gather (communication
+    # stream) and its next reduction (compute stream) in flight at the same time
+    comm = Comm(rank, world, lib.liger_model_comm_bytes(C.byref(cfg), world), channels=2 * cfg.workspace_slots)
     model = C.c_void_p()
     liger.check(lib.liger_model_create(C.byref(model), C.byref(cfg), rank, world, comm.handle))
     x = dev_fill(liger, M, H, 0, 0x10000)
@@ -149,14 +151,38 @@ def _tp_worker(rank, world, port, case, results):
     assert torch.equal(hpart[lo:hi], out.cpu()[lo:hi])
     assert not hpart[:lo].any() and not hpart[hi:].any()
     liger.check(lib.liger_model_set_output_sharding(model, 0))
-    # the batch split into two interleaved micro-requests gives the same bits
+    # the batch split into two micro-requests gives the same bits, with either way of sharing the GPU: 1 = one
+    # compute stream + copy-engine all-gathers underneath (the default), 0 = one stream per micro-request
     if c["B"] % 2 == 0:
         liger.check(lib.liger_model_set_micro_batches(model, 2))
-        out2 = torch.zeros_like(out)
-        for rep in range(2):
-            n2 = liger.check(lib.liger_model_forward(model, ptr(x), ptr(out2), c["B"], c["S"], 0, stream_ptr()))
+        for overlap in (1, 0):
+            liger.check(lib.liger_model_set_overlap(model, overlap))
+            out2 = torch.zeros_like(out)
+            for rep in range(2):
+                liger.check(lib.liger_model_forward(model, ptr(x), ptr(out2), c["B"], c["S"], 0, stream_ptr()))
+                torch.cuda.synchronize()
+            assert torch.equal(out2, out), f"micro-batches (overlap mode {overlap}) differ from the un-split pass"
+        liger.check(lib.liger_model_set_overlap(model, 1))
+        # per-kernel timing inside the pipelined pass does not change the result
+        liger.check(lib.liger_model_set_kernel_timing(model, 1))
+        out3 = torch.zeros_like(out)
+        liger.check(lib.liger_model_forward(model, ptr(x), ptr(out3), c["B"], c["S"], 2, stream_ptr()))
+        kms, kcnt, ov = (C.c_double * 9)(), (C.c_longlong * 9)(), (C.c_double * 4)()
+        liger.check(lib.liger_model_kernel_times(model, C.byref(kms), C.byref(kcnt)))
+        liger.check(lib.liger_model_overlap_times(model, C.byref(ov)))
+        liger.check(lib.liger_model_set_kernel_timing(model, 0))
+        assert torch.equal(out3, out)
+        assert kcnt[0] == 2 * c["layer_num"] and kcnt[3] == 2 * c["layer_num"]   # both micro-requests, every layer
+        # round-robin slots (-1) with two micro-batches on four slots: pairs (0,1), (2,3), (0,1), ... never overlap
+        # and never run past the last slot, however often the host-buffer entry point is called
+        hrr = torch.zeros((M, H), dtype=torch.float16).pin_memory()
+        for rep in range(5):
+            liger.check(lib.liger_model_forward_host(model, C.c_void_p(hin.data_ptr()), C.c_void_p(hrr.data_ptr()), c["B"],
+                                                     c["S"], -1, stream_ptr()))
             torch.cuda.synchronize()
-        assert torch.equal(out2, out), "interleaved micro-batches differ from the un-split pass"
+        if rank == 0:
+            assert torch.equal(hrr, out.cpu())
+        assert lib.liger_model_set_micro_batches(model, 5) == -1   # more micro-batches than workspace slots
         liger.check(lib.liger_model_set_micro_batches(model, 1))
     st = (C.c_uint * 4)()
     assert lib.liger_device_status(C.byref(st)) == 0, list(st)
@@ -209,3 +235,81 @@ def test_decode_step_single_gpu(gpu, liger, oracle, B, kv_len, cap, heads, D, F,
     assert torch.isfinite(out2.float()).all() and not torch.equal(out2, out)
     assert gpu.liger_model_decode(model, ptr(x), ptr(out), B, cap, 0, stream_ptr()) == -1   # cache full
     gpu.liger_model_destroy(model)
+
+
+def _decode_tp_worker(rank, world, port, results):
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, HERE)
+    sys.path.insert(0, os.path.dirname(HERE))
+    from conftest import load_package
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    liger = load_package()
+    from liger_b200.dist import Comm
+    lib = liger.lib()
+    B, kv_len, cap, heads, D, F = DECODE_TP["B"], DECODE_TP["kv_len"], DECODE_TP["cap"], DECODE_TP["heads"], DECODE_TP["D"], DECODE_TP["F"]
+    H = heads * D
+    cfg = liger.default_config(max_batch_size=B, max_seq_len=8, head_num=heads, size_per_head=D, layer_num=2, graph=1, act=1,
+                               ffn_inner=F, causal=1, seed=0, workspace_slots=2, schedule_deep=1, kv_capacity=cap)
+    comm = Comm(rank, world, lib.liger_model_comm_bytes(C.byref(cfg), world), channels=4)
+    model = C.c_void_p()
+    liger.check(lib.liger_model_create(C.byref(model), C.byref(cfg), rank, world, comm.handle))
+    liger.check(lib.liger_model_fill_kv_cache(model))
+    x = dev_fill(liger, B, H, 0, 0x10000)
+    out = torch.zeros((B, H), dtype=torch.float16, device="cuda")
+    dist.barrier()
+    liger.check(lib.liger_model_decode(model, ptr(x), ptr(out), B, kv_len, 0, stream_ptr()))
+    torch.cuda.synchronize()
+    st = (C.c_uint * 4)()
+    assert lib.liger_device_status(C.byref(st)) == 0, list(st)
+    results[rank] = to_np(out)
+    dist.barrier()
+    lib.liger_model_destroy(model)
+    comm.close()
+    dist.destroy_process_group()
+
+
+DECODE_TP = dict(B=4, kv_len=300, cap=512, heads=8, D=128, F=2048)
+
+
+def test_decode_step_tensor_parallel_2(oracle):
+    """BASELINE config 3 in miniature at TP = 2: KV cache sharded by head, one-shot all-reduce of the [B, H] partials."""
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    mgr = mp.Manager()
+    results = mgr.dict()
+    mp.spawn(_decode_tp_worker, args=(2, 29547, results), nprocs=2, join=True)
+    d = DECODE_TP
+    H = d["heads"] * d["D"]
+    x = oracle.fill_normal(d["B"] * H, 0, oracle.INPUT).reshape(d["B"], H)
+    for tp in (2, 1):
+        ocfg = oracle.Config(hidden=H, heads=d["heads"], head_dim=d["D"], ffn_inner=d["F"], layers=2, tp=tp, graph=1, act=1,
+                             causal=1, round16=0, seed=0)
+        want = oracle.stack_decode(ocfg, x, d["B"], d["kv_len"], d["cap"])
+        for r in range(2):
+            assert_close(results[r], want, rel=1e-2, what=f"decode TP=2 rank {r} vs oracle tp={tp}")
+    assert np.array_equal(results[0], results[1])
+
+
+def test_model_destroy_returns_device_memory(gpu, liger):
+    """liger_model_destroy frees weights, workspaces, caches and staging buffers (the reference never frees)."""
+    import torch
+    cfg = liger.default_config(max_batch_size=4, max_seq_len=256, head_num=16, size_per_head=64, layer_num=4, graph=1, act=0,
+                               ffn_inner=4096, causal=1, seed=0, workspace_slots=2, schedule_deep=1, kv_capacity=128)
+    torch.cuda.synchronize()
+    free0 = torch.cuda.mem_get_info()[0]
+    held = []
+    for rep in range(3):
+        model = C.c_void_p()
+        liger.check(gpu.liger_model_create(C.byref(model), C.byref(cfg), 0, 1, None))
+        held.append(free0 - torch.cuda.mem_get_info()[0])
+        liger.check(gpu.liger_model_destroy(model))
+    torch.cuda.synchronize()
+    assert min(held) > 100 << 20                       # the model did hold its ~130 MB of weights and buffers
+    assert free0 - torch.cuda.mem_get_info()[0] < 8 << 20   # and gave all of it back (allocator granularity aside)
