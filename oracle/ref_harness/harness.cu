@@ -10,7 +10,11 @@
 //
 //   liger_ref_harness <batch> <seq> <head_num> <size_per_head> <layers> <steps> <warmup> [dump_file]
 //   liger_ref_harness ops <dump_dir>
+//   liger_ref_harness sweep <max_megabytes> <steps>
 //
+// The third form times the reference's collective as it is bound in src/layer/linear.h:55-60 -- an in-place
+// ncclAllReduce (src/layer/func_wrapper.h:40-43) -- followed by its residual kernel add_bias_input
+// (src/cuda/cuda_kernels.cu:438-461) on fp16 tensors from 8 KB to <max_megabytes> MB in powers of two.
 // The second form runs the reference's own kernels and its cuBLAS-backed linear layers one at a time
 // on seeded inputs (tensor ids 0x20000 + ...) and writes each result as raw fp16 to
 // <dump_dir>/<name>.f16, with a manifest of names and shapes on stdout: the per-operator vectors
@@ -216,6 +220,55 @@ static int run_ops(const char* dir, const StaticNvInitParam& SParams) {
   return err == cudaSuccess ? 0 : 4;
 }
 
+// ---- all-reduce + residual sweep ---------------------------------------------------------------------------
+static int run_sweep(size_t max_bytes, int steps, const StaticNvInitParam& SParams) {
+  DynamicNvInitParam DParams;
+  cudaStream_t st = DParams.stream;
+  const int ws = SParams.world_size, rank = SParams.world_rank;
+  __half *output = dalloc(max_bytes / 2), *input = dalloc(max_bytes / 2), *bias = dalloc(8192);
+  fill_const<<<64, 256, 0, st>>>(bias, 8192, 0.0f);
+  cudaEvent_t e0, e1;
+  cudaEventCreate(&e0); cudaEventCreate(&e1);
+  std::string recs;
+  for (size_t bytes = 8192; bytes <= max_bytes; bytes *= 2) {
+    const int n = bytes >= ((size_t)1 << 20) ? 8192 : 1024;
+    const int m = (int)(bytes / (2 * (size_t)n));
+    fw(output, m, n, 0, 0, n, 600u + (uint32_t)rank, 0.0f, 1.0f);
+    fw(input, m, n, 0, 0, n, 610u, 0.0f, 1.0f);
+    int iters = steps * 4;
+    if (bytes > ((size_t)64 << 20)) { iters = (int)(2000000000ull / bytes); if (iters > steps * 4) iters = steps * 4; if (iters < 3) iters = 3; }
+    auto once = [&]() {
+      Allreduce(output, output, (size_t)m * n, SParams.nccldatatype, ncclSum, SParams.comm, DParams);
+      add_bias_input_kernelLauncher<__half>(output, bias, input, m, n, st);
+    };
+    for (int i = 0; i < 3; ++i) once();
+    // (the reference reduces in place, so repeated launches overflow fp16 after a few sums; the time of neither
+    // kernel depends on the values)
+    cudaStreamSynchronize(st);
+    cudaDeviceSynchronize();
+    MPI_Barrier(MPI_COMM_WORLD);
+    cudaEventRecord(e0, st);
+    for (int i = 0; i < iters; ++i) once();
+    cudaEventRecord(e1, st);
+    cudaEventSynchronize(e1);
+    float ms = 0.0f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    MPI_Barrier(MPI_COMM_WORLD);
+    const double us = 1e3 * ms / iters;
+    char buf[256];
+    snprintf(buf, sizeof(buf), "%s{\"bytes\": %zu, \"rows\": %d, \"cols\": %d, \"us\": %.3f, \"bus_gbs\": %.3f, \"iters\": %d}",
+             recs.empty() ? "" : ", ", bytes, m, n, us, 2.0 * (ws - 1) / ws * (double)bytes / (us * 1e-6) / 1e9, iters);
+    recs += buf;
+  }
+  const cudaError_t err = cudaDeviceSynchronize();
+  if (rank == 0) {
+    printf("{\"ref_sweep\": true, \"world_size\": %d, \"cuda_error\": \"%s\", \"records\": [%s]}\n", ws, cudaGetErrorString(err),
+           recs.c_str());
+    fflush(stdout);
+  }
+  return err == cudaSuccess ? 0 : 4;
+}
+
 int main(int argc, char* argv[]) {
   if (argc == 3 && std::string(argv[1]) == "ops") {
     int ws = 1, wr = 0;
@@ -225,9 +278,17 @@ int main(int argc, char* argv[]) {
     MPI_Finalize();
     return rc;
   }
+  if (argc == 4 && std::string(argv[1]) == "sweep") {
+    int ws = 1, wr = 0;
+    ncclComm_t nc = createNcclComm(argc, argv, ws, wr);
+    StaticNvInitParam SP(wr, ws, nc, 1);
+    const int rc = run_sweep((size_t)atoi(argv[2]) << 20, atoi(argv[3]), SP);
+    MPI_Finalize();
+    return rc;
+  }
   if (argc < 8) {
-    fprintf(stderr, "usage: %s batch seq head_num size_per_head layers steps warmup [dump_file]\n       %s ops dump_dir\n", argv[0],
-            argv[0]);
+    fprintf(stderr, "usage: %s batch seq head_num size_per_head layers steps warmup [dump_file]\n       %s ops dump_dir\n       %s sweep max_megabytes steps\n", argv[0],
+            argv[0], argv[0]);
     return 2;
   }
   int batch = atoi(argv[1]), seq = atoi(argv[2]), head_num = atoi(argv[3]), size_per_head = atoi(argv[4]);
