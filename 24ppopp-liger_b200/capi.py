@@ -6,7 +6,7 @@ from .build import LIB_PATH
 
 LIGER_OK = 0
 EPI_STORE, EPI_GELU, EPI_GEGLU, EPI_QKV_SPLIT, EPI_RESIDUAL, EPI_SCATTER = 0, 1, 2, 3, 4, 5
-DEV_TIMEOUT, DEV_BOUNDS = 1, 2
+DEV_TIMEOUT = 1
 
 
 class LigerError(RuntimeError):

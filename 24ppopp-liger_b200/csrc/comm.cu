@@ -100,6 +100,8 @@ __global__ void allreduce_entry_barrier_kernel(CommDev c, int channel, uint32_t 
   if (threadIdx.x == 0) { stamps[0] = t_enter; stamps[1] = globaltimer_ns(); stamps[4] += stamps[1] - t_enter; }
 }
 
+// VEC = 16-byte vectors per thread a row needs (n <= 256 * VEC * 8 columns); the row lives in registers.
+template <int VEC>
 __global__ void __launch_bounds__(kArThreads, 2)
 allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t recv_off, size_t out_off,
                        const __half* residual_in, __half* hidden,
@@ -107,22 +109,30 @@ allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t recv_o
                        const __half* __restrict__ beta, int n, int row_lo, int row_hi, int one_shot, int rows_per_rank,
                        uint32_t epoch_in,
                        uint32_t epoch_out, unsigned int* done_counter, unsigned long long* stamps, DeviceStatus* st,
-                       int skip_exit_barrier) {
+                       int barrier_mode) {  // 0: exit barrier only (entry ran as its own kernel); 1: no exit barrier; 2: entry barrier here too
   __shared__ float red[32];
   __shared__ int s_fail;
   __shared__ int s_last;
   if (threadIdx.x == 0) { s_fail = 0; s_last = 0; }
   __syncthreads();
 
-  // (the entry barrier ran as allreduce_entry_barrier_kernel, earlier on this stream)
-  (void)epoch_in;
+  // The entry barrier normally ran as allreduce_entry_barrier_kernel, earlier on this stream.  The latency-bound
+  // one-shot form (barrier_mode == 2) does it here instead and saves a launch: block 0 publishes this rank's
+  // arrival, every block waits for all ranks' arrivals on its own (nothing else is running beside a decode step, so
+  // blocks that spin take nothing from anyone).
+  if (barrier_mode == 2) {
+    const unsigned long long t_enter = globaltimer_ns();
+    if (blockIdx.x == 0) barrier_signal(c, channel, epoch_in);
+    barrier_wait(c, channel, epoch_in, &s_fail, st, 0x200u);
+    if (blockIdx.x == 0 && threadIdx.x == 0) { stamps[0] = t_enter; stamps[1] = globaltimer_ns(); stamps[4] += stamps[1] - t_enter; }
+  }
 
   const int nvec = n >> 3;
   for (int row = row_lo + blockIdx.x; row < row_hi; row += gridDim.x) {
     const size_t roff = (size_t)row * n;
-    float v[kArMaxVec][8];
+    float v[VEC][8];
 #pragma unroll
-    for (int i = 0; i < kArMaxVec; ++i)
+    for (int i = 0; i < VEC; ++i)
 #pragma unroll
       for (int j = 0; j < 8; ++j) v[i][j] = 0.0f;
     // Summation order: starts at rank (row mod ws) and continues cyclically.  It depends only on the
@@ -131,40 +141,73 @@ allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t recv_o
     // which spreads the reads over all links.  Gather mode reads only this rank's own rows.
     const int nsum = one_shot == 2 ? 1 : c.ws;
     const int first = one_shot == 2 ? c.rank : row % c.ws;
-    for (int kx = 0; kx < nsum; ++kx) {
-      int p = first + kx;
-      if (p >= c.ws) p -= c.ws;
-      // mode 3: the producing GEMMs already stored every rank's rows for this owner into local slots
-      // mode 5: the same input, but the finished rows are stored locally only (a copy-engine all-gather follows)
-      // mode 4: peers' rows were copied into local receive slots by the copy engines; own rows are
-      // read from the own partial in place
-      const __half* src =
-          (one_shot == 3 || one_shot == 5) ? reinterpret_cast<const __half*>(c.base[c.rank] + partial_off) +
+    // where rank p's contribution to this row lives
+    // mode 3: the producing GEMMs already stored every rank's rows for this owner into local slots
+    // mode 5: the same input, but the finished rows are stored locally only (a copy-engine all-gather follows)
+    // mode 4: peers' rows were copied into local receive slots by the copy engines; own rows are
+    // read from the own partial in place
+    auto source = [&](int p) -> const __half* {
+      return (one_shot == 3 || one_shot == 5) ? reinterpret_cast<const __half*>(c.base[c.rank] + partial_off) +
                               ((size_t)p * rows_per_rank + (row - c.rank * rows_per_rank)) * n
           : one_shot == 4
               ? (p == c.rank ? reinterpret_cast<const __half*>(c.base[c.rank] + partial_off) + roff
                              : reinterpret_cast<const __half*>(c.base[c.rank] + recv_off) +
                                    ((size_t)p * rows_per_rank + (row - c.rank * rows_per_rank)) * n)
               : reinterpret_cast<const __half*>(c.base[p] + partial_off) + roff;
+    };
+    auto accumulate = [&](float (&acc)[8], const uint4& u) {
+      const __half2* h = reinterpret_cast<const __half2*>(&u);
 #pragma unroll
-      for (int i = 0; i < kArMaxVec; ++i) {
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __half22float2(h[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    };
+    // The loads of two ranks are in flight together (where the registers allow: VEC <= 6), which halves the number
+    // of dependent round trips over NVLink; the additions still happen in the order first, first + 1, ...
+    constexpr bool kPair = VEC <= 6;
+    for (int kx = 0; kx < nsum; kx += kPair ? 2 : 1) {
+      int p0 = first + kx;
+      if (p0 >= c.ws) p0 -= c.ws;
+      const __half* s0 = source(p0);
+      uint4 u0[VEC];
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) {
         const int idx = threadIdx.x + i * kArThreads;
-        if (idx < nvec) {
-          uint4 u = __ldcg(reinterpret_cast<const uint4*>(src + (size_t)idx * 8));
-          const __half2* h = reinterpret_cast<const __half2*>(&u);
+        if (idx < nvec) u0[i] = __ldcg(reinterpret_cast<const uint4*>(s0 + (size_t)idx * 8));
+      }
+      if constexpr (kPair) {
+        const bool two = kx + 1 < nsum;
+        int p1 = first + kx + 1;
+        if (p1 >= c.ws) p1 -= c.ws;
+        const __half* s1 = two ? source(p1) : s0;
+        uint4 u1[VEC];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float2 f = __half22float2(h[j]);
-            v[i][2 * j] += f.x;
-            v[i][2 * j + 1] += f.y;
+        for (int i = 0; i < VEC; ++i) {
+          const int idx = threadIdx.x + i * kArThreads;
+          if (two && idx < nvec) u1[i] = __ldcg(reinterpret_cast<const uint4*>(s1 + (size_t)idx * 8));
+        }
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          const int idx = threadIdx.x + i * kArThreads;
+          if (idx < nvec) {
+            accumulate(v[i], u0[i]);
+            if (two) accumulate(v[i], u1[i]);
           }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+          const int idx = threadIdx.x + i * kArThreads;
+          if (idx < nvec) accumulate(v[i], u0[i]);
         }
       }
     }
     // residual + bias; round to fp16 (the value every later consumer sees)
     float sum = 0.0f;
 #pragma unroll
-    for (int i = 0; i < kArMaxVec; ++i) {
+    for (int i = 0; i < VEC; ++i) {
       const int idx = threadIdx.x + i * kArThreads;
       if (idx < nvec) {
         if (hidden != nullptr) {
@@ -205,7 +248,7 @@ allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t recv_o
       mean = warp_sum(t) / (float)n;
       float vs = 0.0f;
 #pragma unroll
-      for (int i = 0; i < kArMaxVec; ++i) {
+      for (int i = 0; i < VEC; ++i) {
         const int idx = threadIdx.x + i * kArThreads;
         if (idx < nvec) {
 #pragma unroll
@@ -220,7 +263,7 @@ allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t recv_o
       rstd = rsqrtf(warp_sum(t) / (float)n + 1e-6f);
     }
 #pragma unroll
-    for (int i = 0; i < kArMaxVec; ++i) {
+    for (int i = 0; i < VEC; ++i) {
       const int idx = threadIdx.x + i * kArThreads;
       if (idx < nvec) {
         uint4 o;
@@ -261,7 +304,7 @@ allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t recv_o
     if (ticket == gridDim.x - 1) { *done_counter = 0u; s_last = 1; }
   }
   __syncthreads();
-  if (s_last && skip_exit_barrier) {
+  if (s_last && barrier_mode == 1) {
     if (threadIdx.x == 0) { stamps[2] = globaltimer_ns(); stamps[5] += stamps[2] - stamps[1]; stamps[7] += 1ull; }
   } else if (s_last) {
     const unsigned long long t_work = globaltimer_ns();
@@ -284,6 +327,16 @@ using namespace liger;
 namespace liger {
 __global__ void comm_barrier_kernel(CommDev c, int channel, uint32_t epoch, unsigned long long* stamps, int stamp_slot,
                                     DeviceStatus* st, unsigned int where);
+}
+
+// Launches the instance whose per-thread row buffer just fits n columns.
+template <typename... Args>
+static void launch_allreduce_kernel(int grid, cudaStream_t stream, int n, Args... args) {
+  const int vec = (n / 8 + kArThreads - 1) / kArThreads;
+  if (vec <= 2) allreduce_fused_kernel<2><<<grid, kArThreads, 0, stream>>>(args...);
+  else if (vec <= 4) allreduce_fused_kernel<4><<<grid, kArThreads, 0, stream>>>(args...);
+  else if (vec <= 6) allreduce_fused_kernel<6><<<grid, kArThreads, 0, stream>>>(args...);
+  else allreduce_fused_kernel<8><<<grid, kArThreads, 0, stream>>>(args...);
 }
 
 extern "C" int liger_comm_create(liger_comm** out, int rank, int world_size, size_t data_bytes, int channels) {
@@ -457,14 +510,16 @@ extern "C" int liger_allreduce_fused(liger_comm* c, int channel, size_t partial_
   if (grid < 1) grid = 1;
   const uint32_t e_in = ++c->epoch[channel];
   const uint32_t e_out = one_shot == 5 ? e_in : ++c->epoch[channel];  // mode 5 has no exit barrier
-  allreduce_entry_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(cd, channel, e_in, c->stamps + 8 * channel,
-                                                                     dev->status_dev);
-  int rc = check_launch("allreduce_entry_barrier_kernel");
-  if (rc != LIGER_OK) return rc;
-  allreduce_fused_kernel<<<grid, kArThreads, 0, (cudaStream_t)stream>>>(
-      cd, channel, kFlagRegionBytes + partial_off, 0, kFlagRegionBytes + out_off, (const __half*)residual_in, (__half*)hidden, (const __half*)bias,
+  int rc;
+  if (one_shot != 1) {
+    allreduce_entry_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(cd, channel, e_in, c->stamps + 8 * channel,
+                                                                       dev->status_dev);
+    if ((rc = check_launch("allreduce_entry_barrier_kernel")) != LIGER_OK) return rc;
+  }
+  launch_allreduce_kernel(
+      grid, (cudaStream_t)stream, n, cd, channel, kFlagRegionBytes + partial_off, (size_t)0, kFlagRegionBytes + out_off, (const __half*)residual_in, (__half*)hidden, (const __half*)bias,
       (const __half*)gamma, (const __half*)beta, n, lo, hi, one_shot, rpr_all, e_in, e_out, c->done + channel,
-      c->stamps + 8 * channel, dev->status_dev, one_shot == 5 ? 1 : 0);
+      c->stamps + 8 * channel, dev->status_dev, one_shot == 5 ? 1 : one_shot == 1 ? 2 : 0);
   return check_launch("allreduce_fused_kernel");
 }
 
@@ -581,8 +636,8 @@ extern "C" int liger_allreduce_ce(liger_comm* c, int channel, size_t partial_off
   }
   if (grid > max_ctas) grid = max_ctas;
   if (grid < 1) grid = 1;
-  allreduce_fused_kernel<<<grid, kArThreads, 0, s>>>(
-      cd, channel, kFlagRegionBytes + partial_off, kFlagRegionBytes + recv_off, kFlagRegionBytes + out_off,
+  launch_allreduce_kernel(
+      grid, s, n, cd, channel, kFlagRegionBytes + partial_off, kFlagRegionBytes + recv_off, kFlagRegionBytes + out_off,
       (const __half*)residual_in, (__half*)hidden, (const __half*)bias, (const __half*)gamma, (const __half*)beta, n, lo, hi, 4,
       rpr, e_in, e_out, c->done + channel, c->stamps + 8 * channel, dev->status_dev, 1);
   if ((rc = check_launch("allreduce_fused_kernel")) != LIGER_OK) return rc;

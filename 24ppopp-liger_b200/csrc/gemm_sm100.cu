@@ -243,6 +243,7 @@ void choose_tile_order(GemmParams& p, const liger_gemm_args& a, int tile_m, int 
 }
 
 int launch_gemm_2cta(const liger_gemm_args& a, const GemmParams& p0, int sm_count, cudaStream_t stream);
+int launch_gemm_smallm(const liger_gemm_args& a, const GemmParams& p0, const DeviceInfo* dev, cudaStream_t stream);
 
 // 0 = choose automatically, 1 = 1-CTA kernel only, 2 = 2-CTA kernel whenever the shape allows
 static int g_gemm_variant = -1;
@@ -337,6 +338,11 @@ extern "C" int liger_gemm_fp16(const liger_gemm_args* args, void* stream) {
     if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_bn = bn; }
   }
   cudaStream_t s = (cudaStream_t)stream;
+  // a handful of rows (decode): the weight-streaming kernel with swapped operand roles and split K
+  if (a.m <= 32) {
+    const int rcs = launch_gemm_smallm(a, p, dev, s);
+    if (rcs != LIGER_ERR_UNSUPPORTED) return rcs;
+  }
   // 2-CTA 256x256 tiles when there is at least one full wave of them (one tile per SM pair)
   const long tiles2 = (long)((a.m + 255) / 256) * ((span + 255) / 256);
   const int variant = gemm_variant();

@@ -634,10 +634,15 @@ def run_allreduce_sweep(args, env):
                                                          C.c_void_p(bias.data_ptr()), None, None, m, n, 0, m, one_shot, sp))
         for _ in range(3):
             call()
+        t4 = (C.c_double * 4)()
+        liger.check(lib.liger_comm_timing(comm.handle, 0, 1, C.byref(t4)))   # reset the in-kernel stamps
         ms, _, _ = env.timed(call, iters)
         us = ms * 1e3 / iters
+        liger.check(lib.liger_comm_timing(comm.handle, 0, 1, C.byref(t4)))
+        k = max(t4[3], 1.0)
         records.append({"bytes": nbytes, "rows": m, "cols": n, "mode": "one-shot" if one_shot else "two-shot", "us": us,
-                        "bus_gbs": 2.0 * (world - 1) / world * nbytes / (us * 1e-6) / 1e9, "iters": iters})
+                        "bus_gbs": 2.0 * (world - 1) / world * nbytes / (us * 1e-6) / 1e9, "iters": iters,
+                        "in_kernel_us": {"entry_wait": t4[0] / k, "work": t4[1] / k, "exit_wait": t4[2] / k}})
     env.check_device_status()
     if rank == 0:
         best = max(r["bus_gbs"] for r in records)

@@ -32,13 +32,12 @@ extern "C" {
 #define LIGER_ERR_INVALID (-1)     /* bad argument (shape, alignment, null pointer) */
 #define LIGER_ERR_CUDA (-2)        /* a CUDA runtime / driver call failed */
 #define LIGER_ERR_UNSUPPORTED (-3) /* shape outside what the kernels implement */
-#define LIGER_ERR_DEVICE (-4)      /* the sticky device status word is set (timeout, bounds) */
+#define LIGER_ERR_DEVICE (-4)      /* the sticky device status word is set (a device-side wait timed out) */
 #define LIGER_ERR_TOO_LARGE (-5)   /* a fixed-capacity resource is too small for the request */
 #define LIGER_ERR_COMM (-6)        /* communicator set-up failed */
 
 /* bits of the sticky device status word */
 #define LIGER_DEV_TIMEOUT 1u /* a bounded device-side wait ran out */
-#define LIGER_DEV_BOUNDS 2u  /* an index check inside a kernel failed; the access was skipped */
 
 /* Message describing the last error returned to the calling thread ("" if none). */
 LIGER_API const char* liger_last_error(void);
@@ -47,8 +46,9 @@ LIGER_API const char* liger_last_error(void);
 LIGER_API const char* liger_version(void);
 
 /*
- * Sticky device status.  Kernels never trap or spin forever: a wait that exceeds its budget or
- * an index that fails a check sets a bit in a host-visible status word and the kernel unwinds.
+ * Sticky device status.  Kernels never trap or spin forever: a wait that exceeds its budget sets a bit
+ * in a host-visible status word and the kernel unwinds.  (Shapes, strides, alignment and buffer extents are
+ * checked on the host before a launch; kernels carry no index checks of their own.)
  * out[0] = LIGER_DEV_* bits, out[1] = location id, out[2..3] = detail.  Returns out[0].
  * The reference ignores every CUDA / cuBLAS / NCCL return code (e.g. src/layer/func_wrapper.h:25,42).
  */

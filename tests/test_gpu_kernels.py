@@ -166,6 +166,97 @@ def test_gemm_residual(gpu, liger, oracle):
     assert_close(to_np(out), want, rel=1e-2, what="gemm+residual")
 
 
+@pytest.mark.parametrize("epi", ["store", "gelu", "residual", "geglu", "qkv", "qkv_cache"])
+@pytest.mark.parametrize("m,k", [(32, 1024), (4, 136), (1, 4096), (17, 520)])
+def test_gemm_few_rows_weight_streaming_kernel(gpu, liger, oracle, epi, m, k):
+    """M <= 32 (a decode step) runs on the weight-streaming kernel: operand roles swapped (128 features x 32
+    tokens per accumulator), K split over a thread-block cluster and summed through distributed shared memory.
+    Every epilogue kind against the oracle, with K that is not a multiple of the 64-deep k-block, N that is not
+    a multiple of the 128-feature tile, and M below the 32-token tile."""
+    import torch
+    code = {"store": 0, "gelu": liger.capi.EPI_GELU, "residual": liger.capi.EPI_RESIDUAL, "geglu": liger.capi.EPI_GEGLU,
+            "qkv": liger.capi.EPI_QKV_SPLIT, "qkv_cache": liger.capi.EPI_QKV_SPLIT}[epi]
+    a = dev_fill(liger, m, k, 0, 400)
+    if epi == "geglu":
+        f = 416                      # 2f = 832 interleaved rows: 6.5 feature tiles
+        wt = torch.zeros((2 * f, k), dtype=torch.float16, device="cuda")
+        dev_fill(liger, k, f, 0, 401, col0=0, src_ld=2 * f, std=0.02, mode=2, out=wt)
+        dev_fill(liger, k, f, 0, 401, col0=f, src_ld=2 * f, std=0.02, mode=3, out=wt)
+        b_full = oracle.fill_normal(2 * f, 0, 402, std=0.02)
+        b_il = np.empty(2 * f, np.float32)
+        for j in range(f):
+            b_il[(j // 32) * 64 + j % 32] = b_full[j]
+            b_il[(j // 32) * 64 + 32 + j % 32] = b_full[f + j]
+        out = gemm(liger, a, wt, epi=code, bias=t16(b_il))
+        w = oracle.fill_window(k, 2 * f, 0, 0, 2 * f, 0, 401, 0.0, 0.02)
+        want = oracle.add_bias_geglu(oracle.linear(to_np(a), w), b_full)
+        assert_close(to_np(out), want, rel=1e-2, what=f"few-row gemm {epi}")
+    elif epi.startswith("qkv"):
+        h, D, S = 5, 64, 1           # n = 960: 7.5 feature tiles; one token per sequence
+        n = 3 * h * D
+        wt = dev_fill(liger, k, n, 0, 401, std=0.02, mode=1)
+        bias = dev_fill(liger, 1, n, 0, 402, std=0.02).reshape(-1)
+        lin = oracle.linear(to_np(a), to_np(wt).T)
+        parts = [oracle.add_bias_split_heads(lin[:, i * h * D:(i + 1) * h * D], to_np(bias)[i * h * D:(i + 1) * h * D], m, S, h, D)
+                 for i in range(3)]
+        if epi == "qkv":
+            qkv = [torch.zeros((m, h, S, D), dtype=torch.float16, device="cuda") for _ in range(3)]
+            gemm(liger, a, wt, epi=code, bias=bias, qkv=qkv, seq_len=S, heads=h, head_dim=D)
+            for i in range(3):
+                assert_close(to_np(qkv[i]), parts[i], rel=1e-2, what=f"few-row qkv split {i}")
+        else:                        # K and V appended to a cache at position 7 of 12
+            cap, pos = 12, 7
+            q = torch.zeros((m, h, S, D), dtype=torch.float16, device="cuda")
+            kc = torch.zeros((m, h, cap, D), dtype=torch.float16, device="cuda")
+            vc = torch.zeros_like(kc)
+            args = liger.GemmArgs()
+            args.a, args.wt, args.bias = a.data_ptr(), wt.data_ptr(), bias.data_ptr()
+            args.m, args.n, args.k, args.lda, args.ldw = m, n, k, k, k
+            args.n_begin, args.n_end, args.epilogue = 0, n, code
+            args.q_out, args.k_out, args.v_out = q.data_ptr(), kc.data_ptr(), vc.data_ptr()
+            args.seq_len, args.heads, args.head_dim, args.kv_stride, args.kv_pos = S, h, D, cap, pos
+            liger.check(liger.lib().liger_gemm_fp16(C.byref(args), stream_ptr()))
+            assert_close(to_np(q), parts[0], rel=1e-2, what="few-row q")
+            assert_close(to_np(kc)[:, :, pos:pos + 1], parts[1], rel=1e-2, what="few-row k append")
+            assert_close(to_np(vc)[:, :, pos:pos + 1], parts[2], rel=1e-2, what="few-row v append")
+            assert not to_np(kc)[:, :, :pos].any() and not to_np(kc)[:, :, pos + 1:].any()
+    else:
+        n = 1096                     # 8.56 feature tiles
+        wt = dev_fill(liger, k, n, 0, 401, std=0.02, mode=1)
+        bias = dev_fill(liger, 1, n, 0, 402, std=0.02).reshape(-1)
+        res = dev_fill(liger, m, n, 0, 403) if epi == "residual" else None
+        out = gemm(liger, a, wt, epi=code, bias=bias, residual=res)
+        want = oracle.linear(to_np(a), to_np(wt).T) + to_np(bias)[None, :]
+        if epi == "gelu":
+            want = oracle.add_bias_gelu(want, None)
+        if epi == "residual":
+            want = want + to_np(res)
+        assert_close(to_np(out), want, rel=1e-2, what=f"few-row gemm {epi}")
+        assert max_rel_err(to_np(out), want) < 2e-3      # fp32 accumulation: only the final rounding is left
+        # slices of the feature range give the bits of the whole launch (the K split is chosen from the whole weight)
+        out2 = torch.zeros_like(out)
+        for lo, hi in [(0, 136), (136, 512), (512, n)]:
+            gemm(liger, a, wt, epi=code, bias=bias, residual=res, n_begin=lo, n_end=hi, out=out2)
+        assert torch.equal(out2, out)
+    check_status(liger)
+
+
+def test_gemm_few_rows_at_decode_shapes(gpu, liger):
+    """The four GEMM shapes of a GLM-130B decode step at TP = 8 (32 tokens): sampled entries against fp64 dot products."""
+    import torch
+    for (n, k) in [(4608, 12288), (12288, 1536), (8192, 12288), (12288, 4096)]:
+        a = dev_fill(liger, 32, k, 0, 410, std=0.5)
+        wt = dev_fill(liger, k, n, 0, 411, std=0.02, mode=1)
+        y = gemm(liger, a, wt)
+        check_status(liger)
+        g = torch.Generator().manual_seed(1)
+        rows = torch.randint(0, 32, (48,), generator=g).tolist()
+        cols = torch.randint(0, n, (48,), generator=g).tolist() + [0, n - 1]
+        for r, c in zip(rows + [0, 31], cols):
+            want = (a[r].double() * wt[c].double()).sum().item()
+            assert abs(y[r, c].item() - want) <= 2e-3 * max(1.0, abs(want)), (n, k, r, c)
+
+
 def test_gemm_linearity_at_full_size(gpu, liger):
     """Size-independent property at the GLM-130B TP=8 QKV shape: (A1 + A2) W == A1 W + A2 W up to
     fp16 rounding, and a sampled set of entries against an fp64 dot product."""
