@@ -25,6 +25,7 @@ class GemmArgs(C.Structure):
         ("seq_len", C.c_int), ("heads", C.c_int), ("head_dim", C.c_int),
         ("kv_stride", C.c_int), ("kv_pos", C.c_int),
         ("scatter_comm", C.c_void_p), ("scatter_off", C.c_size_t),
+        ("gather_comm", C.c_void_p), ("gather_channel", C.c_int),
     ]
 
 
@@ -36,7 +37,7 @@ class ModelConfig(C.Structure):
                                        "kernel_num", "factor", "rq_interval", "graph", "act", "ffn_inner", "causal")] + \
                [("seed", C.c_uint32), ("num_requests", C.c_int), ("ignore_num", C.c_int), ("schedule_deep", C.c_int),
                 ("contention", C.c_float), ("poisson", C.c_int), ("min_seq_len", C.c_int), ("seq_round", C.c_int),
-                ("workspace_slots", C.c_int), ("kv_capacity", C.c_int)]
+                ("workspace_slots", C.c_int), ("kv_capacity", C.c_int), ("min_slice_efficiency", C.c_float)]
 
 
 class ServingMetrics(C.Structure):
@@ -95,6 +96,7 @@ SIGNATURES = {
     "liger_comm_world_size": (_I, [_P]),
     "liger_comm_channels": (_I, [_P]),
     "liger_allgather_ce": (_I, [_P, _I, _SZ, _I, _I, _I, _I, _P]),
+    "liger_allgather_push": (_I, [_P, _I, _I, _SZ, _I, _I, _P]),
     "liger_allreduce_ce": (_I, [_P, _I, _SZ, _SZ, _SZ, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "liger_allreduce_fused": (_I, [_P, _I, _SZ, _SZ, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "liger_model_config_init": (None, [C.POINTER(ModelConfig)]),

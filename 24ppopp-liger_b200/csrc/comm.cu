@@ -14,6 +14,7 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <string>
 #include <vector>
 
 #include "comm_internal.h"
@@ -23,7 +24,6 @@ LIGER_REGISTER_WAIT_BUDGET()
 
 namespace liger {
 
-constexpr int kFlagStrideWords = 32;        // one 128-byte line per (channel, peer) flag
 constexpr int kArThreads = 256;
 constexpr int kArMaxVec = 8;
 
@@ -48,15 +48,6 @@ constexpr uint32_t kHandleMagic = 0x4c474843u;
 }  // namespace liger
 
 namespace liger {
-
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
 
 __device__ __forceinline__ uint32_t* flag_ptr(uint8_t* seg_base, int channel, int slot) {
   return reinterpret_cast<uint32_t*>(seg_base) + ((size_t)channel * kMaxRanks + slot) * kFlagStrideWords;
@@ -320,6 +311,10 @@ allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t recv_o
   }
 }
 
+
+// ---- all-gather whose consumer is the next GEMM (liger_allgather_push) ---------------------------------------
+__global__ void set_word_kernel(uint32_t* word, uint32_t value) { *word = value; }
+
 }  // namespace liger
 
 using namespace liger;
@@ -356,15 +351,19 @@ extern "C" int liger_comm_create(liger_comm** out, int rank, int world_size, siz
   if (e == cudaSuccess) e = cudaMemset(c->done, 0, sizeof(unsigned int) * channels);
   if (e == cudaSuccess) e = cudaMalloc((void**)&c->stamps, sizeof(unsigned long long) * 8 * channels);
   if (e == cudaSuccess) e = cudaMemset(c->stamps, 0, sizeof(unsigned long long) * 8 * channels);
+  if (e == cudaSuccess) e = cudaMalloc((void**)&c->ready_src, sizeof(uint32_t) * channels);
+  if (e == cudaSuccess) e = cudaMemset(c->ready_src, 0, sizeof(uint32_t) * channels);
   if (e == cudaSuccess) e = cudaDeviceSynchronize();
   if (e != cudaSuccess) {
     if (c->local) cudaFree(c->local);
     if (c->done) cudaFree(c->done);
     if (c->stamps) cudaFree(c->stamps);
+    if (c->ready_src) cudaFree(c->ready_src);
     delete c;
     return set_error(LIGER_ERR_CUDA, "comm_create: allocating %zu bytes failed: %s", data_bytes, cudaGetErrorString(e));
   }
   c->epoch.assign(channels, 0u);
+  c->ready_block_rows.assign(channels, 0);
   c->peer[rank] = c->local;
   if (world_size == 1) c->connected = true;
   *out = c;
@@ -436,6 +435,10 @@ extern "C" int liger_comm_destroy(liger_comm* c) {
   if (c->local) cudaFree(c->local);
   if (c->done) cudaFree(c->done);
   if (c->stamps) cudaFree(c->stamps);
+  if (c->ready_src) cudaFree(c->ready_src);
+  for (cudaStream_t hs : c->gather_streams) cudaStreamDestroy(hs);
+  for (cudaEvent_t he : c->gather_events) cudaEventDestroy(he);
+  if (c->gather_fork) cudaEventDestroy(c->gather_fork);
   delete c;
   cudaGetLastError();
   return LIGER_OK;
@@ -650,5 +653,80 @@ extern "C" int liger_allreduce_ce(liger_comm* c, int channel, size_t partial_off
                                      cudaMemcpyDefault, s));
   }
   comm_barrier_kernel<<<1, 32, 0, s>>>(cd, channel, e_out, c->stamps + 8 * channel, 6, dev->status_dev, 0x211u);
+  return check_launch("comm_barrier_kernel");
+}
+
+
+// All-gather whose consumer is the next GEMM (liger_gemm_args.gather_comm): see allgather_push_kernel.  The push
+// is followed by a one-warp barrier kernel on barrier_channel, so that work ordered after this call on `stream`
+// (or after an event recorded there) sees every rank's rows, flags or no flags.
+extern "C" int liger_allgather_push(liger_comm* c, int ready_channel, int barrier_channel, size_t out_off, int m, int n,
+                                    void* stream) {
+  if (!c) return set_error(LIGER_ERR_INVALID, "allgather_push: null communicator");
+  if (!c->connected) return set_error(LIGER_ERR_COMM, "allgather_push: communicator is not connected");
+  if (ready_channel < 0 || ready_channel >= c->channels || barrier_channel < 0 || barrier_channel >= c->channels ||
+      ready_channel == barrier_channel)
+    return set_error(LIGER_ERR_INVALID, "allgather_push: channels %d, %d of %d (two different ones)", ready_channel, barrier_channel,
+                     c->channels);
+  if (m <= 0 || n <= 0 || n % 8) return set_error(LIGER_ERR_INVALID, "allgather_push: n = %d must be a positive multiple of 8", n);
+  if (out_off % 16 || out_off + (size_t)m * n * 2 > c->data_bytes)
+    return set_error(LIGER_ERR_INVALID, "allgather_push: region must be 16-byte aligned and inside the %zu-byte data region", c->data_bytes);
+  const DeviceInfo* dev = current_device();
+  if (!dev) return LIGER_ERR_CUDA;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int ws = c->ws, rank = c->rank, rpr = (m + ws - 1) / ws;
+  const int lo = rank * rpr < m ? rank * rpr : m, hi = (rank + 1) * rpr < m ? (rank + 1) * rpr : m;
+  // row blocks of 256 rows (a GEMM tile), more when a rank owns more than 32 of them
+  int block_rows = 256;
+  while ((rpr + block_rows - 1) / block_rows > kReadyBlocksMax) block_rows *= 2;
+  CommDev cd;
+  for (int p = 0; p < kMaxRanks; ++p) cd.base[p] = p < ws ? c->peer[p] : nullptr;
+  cd.rank = rank; cd.ws = ws;
+  const uint32_t e_ready = ++c->epoch[ready_channel];
+  c->ready_block_rows[ready_channel] = block_rows;
+  // The copy engines move the data: per (row block, peer) one peer copy of the rows and one 4-byte peer copy that
+  // publishes the epoch, in stream order.  No SM is involved, so the transfer is indifferent to what the GEMM
+  // beside it occupies.  (A copy kernel on the SMs was tried and dropped: a 10-warp 256x512 GEMM CTA, or a
+  // 6-warp one at 255 registers per thread, leaves two of an SM's four sub-partitions without registers for even
+  // one more warp, so the copy kernel was never scheduled while the GEMM waited for its data.)
+  // The steps are dealt round-robin to a few internal streams so that more than one copy engine works at a time.
+  if (hi > lo && ws > 1) {
+    static int nstreams = -1;
+    if (nstreams < 0) { const char* e = getenv("LIGER_GATHER_STREAMS"); nstreams = (e && atoi(e) >= 1 && atoi(e) <= 4) ? atoi(e) : 2; }
+    while ((int)c->gather_streams.size() < nstreams) {
+      cudaStream_t hs = nullptr;
+      cudaEvent_t he = nullptr;
+      LIGER_CUDA_TRY(cudaStreamCreateWithFlags(&hs, cudaStreamNonBlocking));
+      LIGER_CUDA_TRY(cudaEventCreateWithFlags(&he, cudaEventDisableTiming));
+      c->gather_streams.push_back(hs);
+      c->gather_events.push_back(he);
+    }
+    if (!c->gather_fork) LIGER_CUDA_TRY(cudaEventCreateWithFlags(&c->gather_fork, cudaEventDisableTiming));
+    uint32_t* word = c->ready_src + ready_channel;  // epoch source for the flag copies
+    set_word_kernel<<<1, 1, 0, s>>>(word, e_ready);
+    int rc = check_launch("set_word_kernel");
+    if (rc != LIGER_OK) return rc;
+    LIGER_CUDA_TRY(cudaEventRecord(c->gather_fork, s));
+    for (int h = 0; h < nstreams; ++h) LIGER_CUDA_TRY(cudaStreamWaitEvent(c->gather_streams[h], c->gather_fork, 0));
+    const int nblk = (hi - lo + block_rows - 1) / block_rows;
+    int step = 0;
+    for (int blk = 0; blk < nblk; ++blk) {
+      const int r0 = lo + blk * block_rows, r1 = r0 + block_rows < hi ? r0 + block_rows : hi;
+      const size_t off = kFlagRegionBytes + out_off + (size_t)r0 * n * 2, bytes = (size_t)(r1 - r0) * n * 2;
+      for (int k = 1; k < ws; ++k, ++step) {
+        const int p = (rank - k + ws) % ws;
+        cudaStream_t hs = c->gather_streams[step % nstreams];
+        LIGER_CUDA_TRY(cudaMemcpyAsync(c->peer[p] + off, c->local + off, bytes, cudaMemcpyDefault, hs));
+        uint32_t* flag = reinterpret_cast<uint32_t*>(c->peer[p]) + ((size_t)ready_channel * kMaxRanks + rank) * kFlagStrideWords + blk;
+        LIGER_CUDA_TRY(cudaMemcpyAsync(flag, word, sizeof(uint32_t), cudaMemcpyDefault, hs));
+      }
+    }
+    for (int h = 0; h < nstreams; ++h) {
+      LIGER_CUDA_TRY(cudaEventRecord(c->gather_events[h], c->gather_streams[h]));
+      LIGER_CUDA_TRY(cudaStreamWaitEvent(s, c->gather_events[h], 0));
+    }
+  }
+  const uint32_t e_bar = ++c->epoch[barrier_channel];
+  comm_barrier_kernel<<<1, 32, 0, s>>>(cd, barrier_channel, e_bar, c->stamps + 8 * barrier_channel, 6, dev->status_dev, 0x213u);
   return check_launch("comm_barrier_kernel");
 }

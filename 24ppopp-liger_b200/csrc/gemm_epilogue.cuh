@@ -9,6 +9,7 @@ namespace liger {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int kGemmThreads = 192;
+constexpr int kTmOrderMax = 128;  // row tiles a launch may have for the arrival-order walk (otherwise: plain order)
 
 struct GemmParams {
   __half* c;
@@ -32,11 +33,57 @@ struct GemmParams {
   // 256x512 kernel: tiles [tail_start, tiles) form the last, partly filled wave; with tail_split they
   // run as 256x256 halves, one per CTA pair, which ends that wave in half the time
   int tail_start, tail_split;
+  // A is the result of an all-gather that may still be in flight (liger_allgather_push): row block b of rank o has
+  // landed when word b of flag line o of ready_flags holds ready_epoch or more.  Row tiles are visited in the
+  // order tm_order[] (own rows first, then in arrival order) instead of 0, 1, 2, ...
+  const uint32_t* ready_flags;  // nullptr: A is complete
+  uint32_t ready_epoch;
+  int ready_rpr, ready_rank, ready_block_rows;
+  int tm_order_on;
+  int no_wide;  // host only: keep this launch off the 256x512 kernel
+  uint8_t tm_order[kTmOrderMax];
   DeviceStatus* status;
 };
 
-// host side (gemm_sm100.cu): fills p.stationary / p.panel_tiles
+// The TMA producer of a tile calls this before its first load of A rows [m0, m0 + rows): waits (bounded) until
+// the ranks that own those rows have delivered them.  The flags are written by another GPU's kernel with a
+// system-scope release after its data stores; the acquire load here, followed by a proxy fence, orders this
+// thread's TMA loads (async proxy) behind them.
+__device__ __forceinline__ bool wait_rows_ready(const GemmParams& p, int m0, int rows, volatile uint32_t* abort_flag) {
+  if (p.ready_flags == nullptr || m0 >= p.m) return true;
+  const int last = (m0 + rows < p.m ? m0 + rows : p.m) - 1;
+  bool waited = false;
+  for (int row = m0;;) {
+    const int owner = row / p.ready_rpr;
+    const int blk = (row - owner * p.ready_rpr) / p.ready_block_rows;
+    if (owner != p.ready_rank) {
+      const uint32_t* f = p.ready_flags + (size_t)owner * kFlagStrideWords + blk;
+      unsigned long long t0 = 0;
+      uint32_t spins = 0;
+      while ((int32_t)(ld_acquire_sys(f) - p.ready_epoch) < 0) {
+        if ((++spins & 0x3fu) == 0) {
+          if (*abort_flag) return false;
+          const unsigned long long now = globaltimer_ns();
+          if (t0 == 0) t0 = now;
+          else if (now - t0 > g_wait_budget_ns) { *abort_flag = 1u; return false; }
+        }
+      }
+      waited = true;
+    }
+    // first row of the next (owner, block) piece
+    const int next = owner * p.ready_rpr + (blk + 1) * p.ready_block_rows;
+    const int next_owner = (owner + 1) * p.ready_rpr;
+    row = next < next_owner ? next : next_owner;
+    if (row > last) break;
+  }
+  if (waited) asm volatile("fence.proxy.async;" ::: "memory");
+  return true;
+}
+
+// host side (gemm_sm100.cu): fills p.stationary / p.panel_tiles; and, for an A operand that is still being
+// gathered, p.tm_order / p.tm_order_on
 void choose_tile_order(GemmParams& p, const liger_gemm_args& a, int tile_m, int tile_n);
+void choose_arrival_order(GemmParams& p, int tile_m);
 
 // Tile t of the launch -> (m tile, n tile).  All CTAs walk K in step, so the DRAM traffic of a GEMM
 // is decided by which operand rows the concurrently running tiles share and by what survives in L2
@@ -60,6 +107,7 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, int t, int& tm,
     tm = within / cols;
     tn = panel * p.panel_tiles + (within - tm * cols);
   }
+  if (p.tm_order_on) tm = p.tm_order[tm];
 }
 
 // L2 eviction-priority descriptors for TMA loads (the fixed encodings CUDA's createpolicy produces

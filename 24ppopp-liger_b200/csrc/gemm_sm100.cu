@@ -93,6 +93,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         tile_coords(p, t, tm, tn);
         const int m0 = tm * BM;
         const int n0 = p.n_begin + tn * BN;
+        if (!wait_rows_ready(p, m0, BM, abort_flag)) { ok = false; break; }
         for (int kb = 0; kb < p.kblocks; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
@@ -179,6 +180,7 @@ static int launch_gemm(const liger_gemm_args& a, const GemmParams& p0, int sm_co
   p.tiles_n = (a.n_end - a.n_begin + BN - 1) / BN;
   p.kblocks = (a.k + BK - 1) / BK;
   choose_tile_order(p, a, BM, BN);
+  choose_arrival_order(p, BM);
   CUtensorMap tm_a, tm_b;
   int rc;
   if ((rc = make_tmap_2d_f16(&tm_a, a.a, (uint64_t)a.k, (uint64_t)a.m, (uint64_t)a.lda, BK, BM)) != LIGER_OK) return rc;
@@ -240,6 +242,47 @@ void choose_tile_order(GemmParams& p, const liger_gemm_args& a, int tile_m, int 
     const int panels = (p.tiles_n + p.panel_tiles - 1) / p.panel_tiles;
     p.panel_tiles = (p.tiles_n + panels - 1) / panels;
   }
+}
+
+// A arrives by liger_allgather_push: walk the row tiles (tile_m rows each) in the order their rows land -- this
+// rank's own rows first, then, row block by row block, the blocks of ranks rank+1, rank+2, ... -- in panels of a
+// few row tiles, so that a wave of CTAs needs only the rows that are already there or arrive next.  Launches with
+// more row tiles than the order table holds fall back to the plain order (every tile still waits for its rows).
+void choose_arrival_order(GemmParams& p, int tile_m) {
+  if (p.ready_flags == nullptr) return;
+  const int tiles_m = p.tiles_m;
+  p.tm_order_on = 0;
+  if (tiles_m > kTmOrderMax) return;
+  p.tm_order_on = 1;
+  const int ws = (p.m + p.ready_rpr - 1) / p.ready_rpr;
+  const int steps_per_block = ws > 1 ? ws - 1 : 1;
+  auto step_of_row = [&](int row) -> int {
+    if (row >= p.m) row = p.m - 1;
+    const int owner = row / p.ready_rpr;
+    if (owner == p.ready_rank) return -1;
+    const int blk = (row - owner * p.ready_rpr) / p.ready_block_rows;
+    int k = owner - p.ready_rank;
+    if (k < 0) k += ws;
+    return blk * steps_per_block + (k - 1);
+  };
+  int key[kTmOrderMax];
+  for (int t = 0; t < tiles_m; ++t) {
+    const int a0 = step_of_row(t * tile_m), a1 = step_of_row(t * tile_m + tile_m - 1);
+    key[t] = a0 > a1 ? a0 : a1;
+    p.tm_order[t] = (uint8_t)t;
+  }
+  for (int i = 1; i < tiles_m; ++i) {  // stable insertion sort by arrival step
+    const uint8_t v = p.tm_order[i];
+    int j = i - 1;
+    while (j >= 0 && key[p.tm_order[j]] > key[v]) { p.tm_order[j + 1] = p.tm_order[j]; --j; }
+    p.tm_order[j + 1] = v;
+  }
+  // panels of as many row tiles as one rank owns (at least 2): m runs fastest inside a panel
+  int per_rank = p.ready_rpr / tile_m;
+  if (per_rank < 2) per_rank = 2;
+  if (per_rank > 8) per_rank = 8;
+  p.stationary = 0;
+  p.panel_tiles = per_rank < tiles_m ? per_rank : tiles_m;
 }
 
 int launch_gemm_2cta(const liger_gemm_args& a, const GemmParams& p0, int sm_count, cudaStream_t stream);
@@ -321,6 +364,21 @@ extern "C" int liger_gemm_fp16(const liger_gemm_args* args, void* stream) {
   int rc = require_sm100(&dev);
   if (rc != LIGER_OK) return rc;
   p.status = dev->status_dev;
+  if (a.gather_comm != nullptr) {
+    liger_comm* c = a.gather_comm;
+    if (!c->connected || a.gather_channel < 0 || a.gather_channel >= c->channels || c->ready_block_rows[a.gather_channel] <= 0)
+      return set_error(LIGER_ERR_INVALID, "gemm: gather_comm / gather_channel must name a channel liger_allgather_push has used");
+    p.ready_flags = reinterpret_cast<const uint32_t*>(c->local) + (size_t)a.gather_channel * kMaxRanks * kFlagStrideWords;
+    p.ready_epoch = c->epoch[a.gather_channel];
+    p.ready_rpr = (a.m + c->ws - 1) / c->ws;
+    p.ready_rank = c->rank;
+    p.ready_block_rows = c->ready_block_rows[a.gather_channel];
+    // 256x256 tiles for a consumer of a gather: a wave of them spans half as many row blocks as a wave of 256x512
+    // tiles, so the first wave waits for two ranks' rows instead of six (LIGER_GATHER_WIDE=1 allows the wide kernel)
+    static int gather_wide = -1;
+    if (gather_wide < 0) { const char* e = getenv("LIGER_GATHER_WIDE"); gather_wide = e ? atoi(e) : 0; }
+    p.no_wide = gather_wide ? 0 : 1;
+  }
 
   // Tile-width choice: fewest (waves x per-tile cost); per-tile cost ~ (BM + BN) (operand bytes per
   // k-block and MMA time are both linear in BN).  GeGLU pairs 32-column chunks, so BN >= 64 there.
@@ -339,7 +397,7 @@ extern "C" int liger_gemm_fp16(const liger_gemm_args* args, void* stream) {
   }
   cudaStream_t s = (cudaStream_t)stream;
   // a handful of rows (decode): the weight-streaming kernel with swapped operand roles and split K
-  if (a.m <= 32) {
+  if (a.m <= 32 && p.ready_flags == nullptr) {
     const int rcs = launch_gemm_smallm(a, p, dev, s);
     if (rcs != LIGER_ERR_UNSUPPORTED) return rcs;
   }

@@ -161,6 +161,7 @@ gemm_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         tile_coords(p, t, tm, tn);
         const int m0 = tm * kBM2 + (int)cta_rank * 128;
         const int n0 = p.n_begin + tn * kBN2 + (int)cta_rank * 128;
+        if (!wait_rows_ready(p, m0, 128, abort_flag)) { ok = false; break; }
         for (int kb = 0; kb < p.kblocks; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
@@ -338,6 +339,7 @@ gemm_tcgen05_2cta_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
         const int m0 = w.tm * kBM2 + (int)cta_rank * 128;
         const int n0 = w.n0 + (int)cta_rank * 128;
         const uint32_t tx = 2u * (uint32_t)(Cfg::kABytes + w.halves * Cfg::kBHalfBytes);
+        if (!wait_rows_ready(p, m0, 128, abort_flag)) { ok = false; break; }
         for (int kb = 0; kb < p.kblocks; ++kb) {
           if (!mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
           uint8_t* sa = smem + stage * Cfg::kStageBytes;
@@ -424,7 +426,7 @@ gemm_tcgen05_2cta_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
 constexpr int kStages2 = 6;
 constexpr int kStagesWide = 4;
 
-void choose_tile_order(GemmParams& p, const liger_gemm_args& a, int tile_m, int tile_n);
+// (choose_tile_order / choose_arrival_order: gemm_epilogue.cuh)
 
 // Launches the 2-CTA kernel.  Returns LIGER_ERR_UNSUPPORTED (without touching the error text) when
 // this shape is better served by the 1-CTA kernel.
@@ -445,6 +447,7 @@ static int launch_gemm_2cta_wide(const liger_gemm_args& a, const GemmParams& p0,
   p.tiles_n = (a.n_end - a.n_begin + kBNW - 1) / kBNW;
   p.kblocks = (a.k + BK - 1) / BK;
   choose_tile_order(p, a, kBM2, kBNW);
+  choose_arrival_order(p, kBM2);
   const int tiles = p.tiles_m * p.tiles_n;
   // last wave: when at most half of the CTA pairs would get a tile, split those tiles into halves
   p.tail_start = tiles >= max_clusters ? tiles / max_clusters * max_clusters : tiles;
@@ -481,6 +484,7 @@ int launch_gemm_2cta(const liger_gemm_args& a, const GemmParams& p0, int sm_coun
   p.tiles_n = (a.n_end - a.n_begin + kBN2 - 1) / kBN2;
   p.kblocks = (a.k + BK - 1) / BK;
   choose_tile_order(p, a, kBM2, kBN2);
+  choose_arrival_order(p, kBM2);
   const int tiles = p.tiles_m * p.tiles_n;
   static int max_clusters = -1;
   if (max_clusters < 0) {
@@ -514,7 +518,7 @@ int launch_gemm_2cta(const liger_gemm_args& a, const GemmParams& p0, int sm_coun
     const long cost_w = 2 * full_w + (rem_w == 0 ? 0 : 2 * rem_w <= max_clusters ? 1 : 2);
     const long waves_n = ((long)tiles + max_clusters - 1) / max_clusters;
     const bool geom_ok = a.k >= 8192 && tiles_w >= max_clusters && cost_w <= waves_n + (waves_n + 9) / 10;
-    if (wide_env == 1 || (wide_env < 0 && geom_ok)) return launch_gemm_2cta_wide(a, p0, max_clusters, stream);
+    if (!p0.no_wide && (wide_env == 1 || (wide_env < 0 && geom_ok))) return launch_gemm_2cta_wide(a, p0, max_clusters, stream);
   }
   const int clusters = tiles < max_clusters ? tiles : max_clusters;
   CUtensorMap tm_a, tm_b;

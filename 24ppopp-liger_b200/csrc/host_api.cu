@@ -61,6 +61,7 @@ BertInitParam to_params(const liger_model_config& c) {
   bp.num_requests = c.num_requests; bp.ignore_num = c.ignore_num; bp.schedule_deep = c.schedule_deep;
   bp.contention = c.contention; bp.poisson = c.poisson; bp.min_seq_len = c.min_seq_len; bp.seq_round = c.seq_round;
   bp.workspace_slots = c.workspace_slots; bp.kv_capacity = c.kv_capacity;
+  bp.min_slice_efficiency = c.min_slice_efficiency;
   return bp;
 }
 
@@ -109,6 +110,7 @@ extern "C" void liger_model_config_init(liger_model_config* c) {
   c->seed = d.seed; c->num_requests = d.num_requests; c->ignore_num = d.ignore_num; c->schedule_deep = d.schedule_deep;
   c->contention = d.contention; c->poisson = d.poisson; c->min_seq_len = d.min_seq_len; c->seq_round = d.seq_round;
   c->workspace_slots = d.workspace_slots; c->kv_capacity = d.kv_capacity;
+  c->min_slice_efficiency = d.min_slice_efficiency;
 }
 
 extern "C" size_t liger_model_comm_bytes(const liger_model_config* cfg, int world_size) {
@@ -401,12 +403,120 @@ static int forward_pipelined(liger_model* m, const void* input, void* output, in
   return n;
 }
 
+// The whole batch on the caller's stream, with every bandwidth-bound all-reduce split three ways: the
+// reduce-scatter rode on the row-parallel GEMM's epilogue; the reduction (+ residual + LayerNorm) of the owned
+// rows is a short local kernel; and the all-gather is liger_allgather_push on the communication stream, running
+// beside the NEXT GEMM -- the column-parallel one that consumes the gathered rows -- which is launched at once
+// and waits tile by tile for the row blocks it loads (liger_gemm_args.gather_comm).  No batch splitting, so the
+// GEMMs keep their full-size tile counts; what stays exposed of an all-reduce is the entry barrier, the local
+// reduction, and whatever the first wave of GEMM tiles waits for its rows.
+static int forward_gathered(liger_model* m, const void* input, void* output, int batch, int seq_len, int slot, void* stream) {
+  cudaStream_t s0 = (cudaStream_t)stream;
+  Bert_Model& b = *m->model;
+  if (!m->pipe_comm) {
+    int least = 0, greatest = 0;
+    LIGER_CUDA_TRY(cudaDeviceGetStreamPriorityRange(&least, &greatest));
+    LIGER_CUDA_TRY(cudaStreamCreateWithPriority(&m->pipe_comm, cudaStreamNonBlocking, greatest));
+  }
+  while (m->ev_reduced.empty()) {
+    cudaEvent_t e = nullptr;
+    LIGER_CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    m->ev_reduced.push_back(e);
+    LIGER_CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    m->ev_gather.push_back(e);
+  }
+  cudaStream_t s1 = m->pipe_comm;
+  const int nslots = (int)b.slots.size();
+  const uint8_t* sym = (const uint8_t*)liger_comm_data(m->sp.comm);
+  std::vector<FuncWrap> vec = b.forward(input, output, batch, seq_len, slot);
+  auto begin_rec = [&](cudaStream_t s) -> cudaEvent_t {
+    if (!m->timing) return nullptr;
+    cudaEvent_t e = m->get_event();
+    cudaEventRecord(e, s);
+    return e;
+  };
+  auto end_rec = [&](int name, cudaEvent_t e0, cudaStream_t s) {
+    if (!m->timing) return;
+    cudaEvent_t e1 = m->get_event();
+    cudaEventRecord(e1, s);
+    m->ev_rec.push_back({name, {e0, e1}});
+  };
+  DynamicNvInitParam dp;
+  dp.stream = stream;
+  bool pending = false;  // an all-gather is in flight that nothing on s0 has waited for yet
+  auto settle = [&]() -> int {
+    if (!pending) return LIGER_OK;
+    cudaEvent_t e0 = begin_rec(s0);
+    LIGER_CUDA_TRY(cudaStreamWaitEvent(s0, m->ev_gather[0], 0));
+    end_rec(kWaitRecord, e0, s0);
+    pending = false;
+    return LIGER_OK;
+  };
+  int n = 0, rc;
+  for (size_t i = 0; i < vec.size(); ++i) {
+    const FuncWrap& f = vec[i];
+    const COMM_ARGS& c = f.args_comm_tuple;
+    const bool split = f.type == COMMUNICATION && c.comm != nullptr && c.one_shot == 3 && !c.copy_engine && c.row_begin == 0 &&
+                       c.row_end == c.m;
+    if (!split) {
+      // (a kernel that is not the consumer GEMM never reads a gathered buffer that is still in flight: the only
+      // readers of the all-gather's result are the GEMM below and, after the last layer, the copy-out, for which
+      // the else-branch below has already waited)
+      cudaEvent_t e0 = begin_rec(s0);
+      rc = f.callback(dp);
+      end_rec(f.name, e0, s0);
+      if (rc != LIGER_OK) return rc;
+      ++n;
+      continue;
+    }
+    // the previous gather read this rank's own rows of a buffer the reduction below may overwrite
+    if ((rc = settle()) != LIGER_OK) return rc;
+    cudaEvent_t e0 = begin_rec(s0);
+    rc = liger_allreduce_fused(c.comm, c.channel, c.partial_off, c.out_off, c.residual_in, c.hidden, c.bias, c.gamma, c.beta, c.m,
+                               c.n, 0, c.m, 5, stream);
+    end_rec(f.name, e0, s0);
+    if (rc != LIGER_OK) return rc;
+    LIGER_CUDA_TRY(cudaEventRecord(m->ev_reduced[0], s0));
+    LIGER_CUDA_TRY(cudaStreamWaitEvent(s1, m->ev_reduced[0], 0));
+    const int ready_channel = 2 * nslots + c.channel;
+    e0 = begin_rec(s1);
+    rc = liger_allgather_push(c.comm, ready_channel, nslots + c.channel, c.out_off, c.m, c.n, s1);
+    end_rec(kGatherRecord, e0, s1);
+    if (rc != LIGER_OK) return rc;
+    LIGER_CUDA_TRY(cudaEventRecord(m->ev_gather[0], s1));
+    pending = true;
+    n += 2;
+    const bool consumer_is_gemm = i + 1 < vec.size() && vec[i + 1].type == GEMM &&
+                                  vec[i + 1].args_gemm_tuple.a == (const void*)(sym + c.out_off) &&
+                                  vec[i + 1].args_gemm_tuple.m == c.m && vec[i + 1].args_gemm_tuple.lda == c.n;
+    if (consumer_is_gemm) {
+      GEMM_ARGS g = vec[i + 1].args_gemm_tuple;
+      g.gather_comm = c.comm;
+      g.gather_channel = ready_channel;
+      e0 = begin_rec(s0);
+      rc = liger_gemm_fp16(&g, stream);
+      end_rec(vec[i + 1].name, e0, s0);
+      if (rc != LIGER_OK) return rc;
+      ++n;
+      ++i;
+    } else if ((rc = settle()) != LIGER_OK) {
+      return rc;
+    }
+  }
+  if ((rc = settle()) != LIGER_OK) return rc;
+  return n;
+}
+
 extern "C" int liger_model_forward(liger_model* m, const void* input, void* output, int batch, int seq_len, int slot,
                                    void* stream) {
   if (!m || !input || !output) return liger::set_error(LIGER_ERR_INVALID, "model_forward: null argument");
   try {
     const int mb = m->micro_batches;
     Bert_Model& b = *m->model;
+    if (m->overlap == 2 && m->sp.world_size > 1 && liger_comm_channels(m->sp.comm) >= 3 * (int)b.slots.size()) {
+      if ((slot = pick_slots(b, slot, 1, "model_forward")) < 0) return slot;
+      return forward_gathered(m, input, output, batch, seq_len, slot, stream);
+    }
     if (mb > 1 && m->sp.world_size > 1 && batch % mb == 0) {
       const bool pipelined = m->overlap == 1 && liger_comm_channels(m->sp.comm) >= 2 * (int)b.slots.size();
       if (pipelined || !m->timing) {
@@ -486,7 +596,7 @@ extern "C" int liger_model_set_micro_batches(liger_model* m, int micro_batches) 
 }
 
 extern "C" int liger_model_set_overlap(liger_model* m, int mode) {
-  if (!m || mode < 0 || mode > 1) return liger::set_error(LIGER_ERR_INVALID, "model_set_overlap: 0 or 1");
+  if (!m || mode < 0 || mode > 2) return liger::set_error(LIGER_ERR_INVALID, "model_set_overlap: 0, 1 or 2");
   m->overlap = mode;
   return LIGER_OK;
 }
@@ -591,7 +701,8 @@ extern "C" int liger_model_forward_host(liger_model* m, const void* host_input, 
   const size_t bytes = (size_t)M * H * 2;
   cudaStream_t s = (cudaStream_t)stream;
   // the pass below runs `need` micro-batches on consecutive slots: choose them here, once
-  const int need = (m->micro_batches > 1 && ws > 1 && batch % m->micro_batches == 0) ? m->micro_batches : 1;
+  const bool gathered = m->overlap == 2 && ws > 1 && liger_comm_channels(m->sp.comm) >= 3 * (int)b.slots.size();
+  const int need = (!gathered && m->micro_batches > 1 && ws > 1 && batch % m->micro_batches == 0) ? m->micro_batches : 1;
   if ((slot = pick_slots(b, slot, need, "model_forward_host")) < 0) return slot;
   if (ws == 1) {
     try {
@@ -829,6 +940,8 @@ extern "C" int liger_sim_serve_rank(const liger_model_config* cfg, const liger_s
         }
       }
     scheduler.set_requests(reqs);
+    // contention == 0: measure the two factors on the simulated device, as a profile run does on a real one
+    if (cfg->contention == 0.0f && !reqs.empty()) scheduler.calibrate_contention(reqs.back().batch_size, reqs.back().seq_len);
     if (mode == LIGER_MODE_SCHEDULE) scheduler.run_stream_sync();
     else if (mode == LIGER_MODE_NO_SCHEDULE) scheduler.run_sequential();
     else return liger::set_error(LIGER_ERR_INVALID, "sim_serve: unknown mode %d", mode);

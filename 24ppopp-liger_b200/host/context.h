@@ -63,7 +63,9 @@ struct BertInitParam {
   int num_requests = 150;   // src/schedule.h:295
   int ignore_num = 20;      // src/schedule.h:327
   int schedule_deep = 6;    // src/schedule.h:30
-  float contention = 0.8f;  // src/schedule.h:249
+  float contention = 0.8f;  // src/schedule.h:249; 0 -> the two factors the profile run derived (Scheduler::calibrate_contention)
+  float min_slice_efficiency = 0.0f;  // a GEMM slice is used only if it runs at this fraction of the whole kernel's rate
+                                      // (0: every slice that fits, as the reference, src/init.h:226-259)
   int poisson = 0;          // 0: fixed-interval arrivals (src/schedule.h:301), 1: exponential gaps
   int min_seq_len = 16;     // src/schedule.h:298 draws rand() % (max_seq_len - 28) + 16
   int seq_round = 4;        // request lengths are rounded up to a multiple of this

@@ -3,7 +3,7 @@
 //   liger_mpirun -np N ./liger_main max_batch max_seq head_num size_per_head layer_num kernel_num factor arr_rate
 //                [--mode profile,schedule,no_schedule] [--graph ref|preln] [--act gelu|geglu] [--ffn F]
 //                [--causal 0|1] [--requests R] [--ignore I] [--poisson 0|1] [--seed S] [--seq-round Q]
-//                [--min-seq L] [--contention C] [--depth D]
+//                [--min-seq L] [--contention C|auto] [--min-slice-eff E] [--depth D]
 //
 // The eight positional integers are the reference's (its argv parsing is commented out and the
 // values hard-coded, main.cu:14-31; defaults here are the same: 2 128 128 96 4 16 8 80).  kernel_num is
@@ -46,7 +46,8 @@ int main(int argc, char* argv[]) {
     else if (a == "--seed") bp.seed = (uint32_t)atoi(next("--seed"));
     else if (a == "--seq-round") bp.seq_round = atoi(next("--seq-round"));
     else if (a == "--min-seq") bp.min_seq_len = atoi(next("--min-seq"));
-    else if (a == "--contention") bp.contention = (float)atof(next("--contention"));
+    else if (a == "--contention") { const std::string v = next("--contention"); bp.contention = v == "auto" ? 0.0f : (float)atof(v.c_str()); }
+    else if (a == "--min-slice-eff") bp.min_slice_efficiency = (float)atof(next("--min-slice-eff"));
     else if (a == "--depth") { bp.schedule_deep = atoi(next("--depth")); bp.workspace_slots = bp.schedule_deep + 1; }
     else if (a[0] != '-' && npos < 8) vals[npos++] = atoi(a.c_str());
     else { fprintf(stderr, "unknown argument %s\n", a.c_str()); return 2; }

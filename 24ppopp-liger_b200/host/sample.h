@@ -87,6 +87,7 @@ class Sample {
   std::vector<FuncWrap> _SubFuncWrapVec;  // empty, or [slice that fits, remainder]
   int _factor = 0;
   int _remain = 0;  // units of the current GEMM not yet issued
+  float _whole_duration = 0.0f;  // profiled duration of the GEMM being decomposed
   size_t _sub_exe_num = 0;
   Runtime* _rt;
 
@@ -103,6 +104,7 @@ class Sample {
   int id = 0;
   int slot = 0;  // activation workspace of this request
   int launch_errors = 0;
+  float min_slice_efficiency = 0.0f;  // see BertInitParam::min_slice_efficiency
 
   Sample(std::vector<FuncWrap> vec, const SubDict* dict, int batch_size_, int seq_len_, int factor, Runtime* rt)
       : _factor(factor), _rt(rt), FuncWrapVec(std::move(vec)), profiling_decompse_res_dict(dict),
@@ -213,8 +215,9 @@ class Sample {
       auto it = profiling_decompse_res_dict->find({whole.name, batch_size, seq_len});
       if (it == profiling_decompse_res_dict->end() || (int)it->second.size() < _factor - 1) return false;
       const std::vector<float>& vec = it->second;
+      _whole_duration = whole.duration;
       for (int i = _factor - 2; i >= 0; --i) {
-        if (time_planned >= vec[i]) {
+        if (time_planned >= vec[i] && slice_pays(i + 1, vec[i])) {
           _sub_clear();
           const int n_run = i + 1;
           _remain = _factor - n_run;
@@ -232,7 +235,7 @@ class Sample {
     if (it == profiling_decompse_res_dict->end() || (int)it->second.size() < _factor - 1) return false;
     const std::vector<float>& vec = it->second;
     for (int i = _remain - 2; i >= 0; --i) {
-      if (time_planned >= vec[i]) {
+      if (time_planned >= vec[i] && slice_pays(i + 1, vec[i])) {
         const int n_run = i + 1;
         _remain -= n_run;
         _sub_clear();
@@ -242,6 +245,14 @@ class Sample {
       }
     }
     return false;
+  }
+
+  // A slice of n of the kernel's `factor` units that was profiled at slice_ms: worth launching only if it runs at
+  // min_slice_efficiency of the whole kernel's rate or better.  On a GPU whose GEMM tiles are 256 columns wide and
+  // whose persistent grid wants a multiple of 74 tile pairs, a narrow slice can cost several times its share.
+  bool slice_pays(int n, float slice_ms) const {
+    if (min_slice_efficiency <= 0.0f || _whole_duration <= 0.0f || slice_ms <= 0.0f) return true;
+    return _whole_duration * (float)n / (float)_factor >= min_slice_efficiency * slice_ms;
   }
 
   void record_arrival() { sample_arrive = _rt->wall_seconds(); }

@@ -146,10 +146,12 @@ class Scheduler {
                const std::string& sub_filename, int sq_step = 1, int itr = 20) {
     void* start = _rt->create_event();
     void* stop = _rt->create_event();
+    int last_sq = 0;
     for (int i = low_bs; i < high_bs; ++i) {
       for (int j = low_sq; j < high_sq; ++j) {
         if (sq_step > 1 && j % sq_step != 0) continue;
         if ((i * j) % 4 != 0) continue;  // src/schedule.h:88
+        last_sq = j;
         if (SParams.world_rank == 0) printf("Batch Size: %d; Seq_Len: %d; \n", i, j);
         std::vector<FuncWrap> vec = _model->forward(input, output, i, j, 0);
         std::vector<bool> seen(64, false);
@@ -171,11 +173,95 @@ class Scheduler {
         }
       }
     }
+    if (high_bs > low_bs && last_sq > 0) calibrate_contention(high_bs - 1, last_sq);
     if (SParams.world_rank == 0) {
       MainDictToFile(profiling_res_dict, main_filename);
       SubDictToFile(profiling_decompse_res_dict, sub_filename);
     }
     _coord->barrier();
+  }
+
+  // ---- contention factors from measurement ----------------------------------------------------------
+  // The reference scales the time budget of a scheduling window by a constant 0.8 (src/schedule.h:249), found by
+  // hand on V100.  Here the factor is measured, per direction, on the machine the profile is taken on: the longest
+  // GEMM of a request and its all-reduce are run (i) alone -- the profiled durations -- and (ii) at the same
+  // time on the two streams, once with the GEMM as the main segment and all-reduces as secondary work, once the
+  // other way round.  A kernel that takes s times longer when overlapped consumes s times its profiled duration
+  // of a window that is itself stretched by the main kernel's own slow-down, so a window of profiled length T
+  // has room for secondary kernels of profiled length T * s_main / s_secondary: that ratio (clamped to
+  // [0.05, 1]) is the factor.  The two factors and the four slow-downs are stored in the Main profile under
+  // kernel names 100..105 with batch_size = seq_len = 0, where the reference's reader ignores them.
+  static constexpr int kFactorCommUnderComp = 100, kFactorCompUnderComm = 101;
+  void calibrate_contention(int bs, int sq) {
+    std::vector<FuncWrap> vec = _model->forward(input, output, bs, sq, 0);
+    FuncWrap *g = nullptr, *c = nullptr;
+    float tg = 0.0f, tc = 0.0f;
+    for (auto& f : vec) {
+      const float d = lookup_duration(f.name, bs, sq);
+      if (f.type == GEMM && d > tg) { g = &f; tg = d; }
+      if (f.type == COMMUNICATION && c == nullptr) { c = &f; tc = d; }
+    }
+    if (!g || !c || tg <= 0.0f || tc <= 0.0f) return;  // one GPU: nothing to overlap
+    // enough all-reduces, back to back, to outlast the GEMM however much the two slow each other down
+    const int reps_c = std::min(48, std::max(2, (int)std::ceil(4.0f * tg / tc)));
+    void* ev_start[2] = {_rt->create_event(), _rt->create_event()};
+    void* ev_gemm = _rt->create_event();
+    std::vector<void*> ev_ar(reps_c);
+    for (auto& e : ev_ar) e = _rt->create_event();
+    float slow[2][2];  // [experiment][0: GEMM, 1: all-reduce]
+    for (int exp = 0; exp < 2; ++exp) {
+      // exp 0: the GEMM is the main segment (stream 0), all-reduces are secondary (stream 1); exp 1: the reverse
+      const DynamicNvInitParam& dg = exp == 0 ? DParams0 : DParams1;
+      const DynamicNvInitParam& dc = exp == 0 ? DParams1 : DParams0;
+      float best_g = 1e30f, best_c = 1e30f;
+      for (int trial = 0; trial < 3; ++trial) {
+        _rt->device_synchronize();
+        _coord->barrier();
+        _rt->record(ev_start[0], dg.stream);
+        _rt->record(ev_start[1], dc.stream);
+        if (exp == 0) g->callback(dg);
+        for (int r = 0; r < reps_c; ++r) {
+          c->callback(dc);
+          _rt->record(ev_ar[r], dc.stream);
+          if (exp == 1 && r == 0) g->callback(dg);  // the secondary GEMM follows the first main all-reduce
+        }
+        _rt->record(ev_gemm, dg.stream);
+        _rt->event_synchronize(ev_gemm);
+        _rt->event_synchronize(ev_ar[reps_c - 1]);
+        const float t_gemm = _rt->elapsed_ms(ev_start[0], ev_gemm);
+        // all-reduces (whole and a fraction of the one in flight) finished while the GEMM was running
+        float done = 0.0f, prev = 0.0f;
+        for (int r = 0; r < reps_c; ++r) {
+          const float t = _rt->elapsed_ms(ev_start[1], ev_ar[r]);
+          if (t <= t_gemm) { done += 1.0f; prev = t; }
+          else { if (t > prev) done += (t_gemm - prev) / (t - prev); break; }
+        }
+        if (done < 0.05f) done = 0.05f;
+        best_g = std::min(best_g, t_gemm);
+        best_c = std::min(best_c, t_gemm / done);
+      }
+      slow[exp][0] = std::max(1.0f, best_g / tg);
+      slow[exp][1] = std::max(1.0f, best_c / tc);
+    }
+    auto clamp = [](float v) { return v < 0.05f ? 0.05f : v > 1.0f ? 1.0f : v; };
+    profiling_res_dict[{kFactorCommUnderComp, 0, 0}] = clamp(slow[0][0] / slow[0][1]);
+    profiling_res_dict[{kFactorCompUnderComm, 0, 0}] = clamp(slow[1][1] / slow[1][0]);
+    profiling_res_dict[{102, 0, 0}] = slow[0][0];  // GEMM main, its own slow-down
+    profiling_res_dict[{103, 0, 0}] = slow[0][1];  // ... and that of the all-reduces beside it
+    profiling_res_dict[{104, 0, 0}] = slow[1][1];  // all-reduce main, its own slow-down
+    profiling_res_dict[{105, 0, 0}] = slow[1][0];  // ... and that of the GEMM beside it
+    if (SParams.world_rank == 0)
+      printf("Contention factors from measurement: all-reduce under GEMM %.3f (GEMM x%.2f, all-reduce x%.2f); GEMM under "
+             "all-reduce %.3f (all-reduce x%.2f, GEMM x%.2f). \n",
+             profiling_res_dict[{kFactorCommUnderComp, 0, 0}], slow[0][0], slow[0][1],
+             profiling_res_dict[{kFactorCompUnderComm, 0, 0}], slow[1][1], slow[1][0]);
+  }
+  // The factor of a window whose main segment is of class `main_type`: the configured constant, or, with
+  // BertInitParam::contention == 0, the measured one (0.8 where the profile holds none).
+  float contention_factor(layer_type main_type) const {
+    if (BertParams.contention > 0.0f) return BertParams.contention;
+    auto it = profiling_res_dict.find({main_type == COMMUNICATION ? kFactorCompUnderComm : kFactorCommUnderComp, 0, 0});
+    return it != profiling_res_dict.end() ? it->second : 0.8f;
   }
 
   float time_kernel(FuncWrap& f, void* start, void* stop, int itr) {
@@ -215,6 +301,7 @@ class Scheduler {
     Sample* sample = new Sample(std::move(vec), &profiling_decompse_res_dict, batch_size, seq_len, BertParams.factor, _rt);
     sample->id = _next_id++;
     sample->slot = slot;
+    sample->min_slice_efficiency = BertParams.min_slice_efficiency;
     if (arrive_s >= 0.0) sample->sample_arrive = arrive_s;
     main_q.push(sample);
   }
@@ -307,7 +394,7 @@ class Scheduler {
         time_planned += head->dequeue(DParams0, 1, time_planned);
       }
       ++segments;
-      time_planned *= BertParams.contention;  // the contention factor
+      time_planned *= contention_factor(main_type);  // the contention factor
       // fill the window with kernels of the other class from the other in-flight requests
       for (size_t sub = 1; sub < exe_vec.size(); ++sub) {
         Sample* s = exe_vec.at(sub);

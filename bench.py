@@ -336,11 +336,14 @@ def run_prefill(args, env):
     comm = None
     if world > 1:
         from liger_b200.dist import Comm
-        comm = Comm(rank, world, lib.liger_model_comm_bytes(C.byref(cfg), world), channels=2 * slots)
+        comm = Comm(rank, world, lib.liger_model_comm_bytes(C.byref(cfg), world), channels=3 * slots)
     model = C.c_void_p()
     liger.check(lib.liger_model_create(C.byref(model), C.byref(cfg), rank, world, comm.handle if comm else None))
     # with more than one GPU the batch runs as two micro-requests whose all-gathers hide under each other's GEMMs
-    micro = args.micro_batches if args.micro_batches > 0 else (2 if world > 1 else 1)
+    # Default schedule, from measurements on B200 at N = 2, 4, 8: up to 4 GPUs the whole batch with in-line all-reduces
+    # is as fast as either overlapped schedule (overlap removes idle time, the GPU then meets its power cap and the
+    # GEMMs slow down by as much); at 8 GPUs two micro-requests with copy-engine all-gathers are slightly ahead.
+    micro = args.micro_batches if args.micro_batches > 0 else (2 if world >= 8 and args.overlap == 1 else 1)
     liger.check(lib.liger_model_set_micro_batches(model, micro))
     liger.check(lib.liger_model_set_overlap(model, args.overlap))
     sp, stream = env.sp, env.stream
@@ -412,6 +415,13 @@ def run_prefill(args, env):
     liger.check(lib.liger_model_overlap_times(model, C.byref(ov)))
     lib.liger_model_set_kernel_timing(model, 0)
     env.barrier()
+    if os.environ.get("LIGER_BENCH_ALL_RANKS"):   # diagnostics: every rank's per-kernel averages and in-kernel all-reduce split
+        t4 = (C.c_double * 4)()
+        if comm is not None:
+            lib.liger_comm_timing(comm.handle, 0, 0, C.byref(t4))
+        print(f"rank {rank}: " + " ".join(f"k{k}={kms[k] / max(kcnt[k], 1) * 1e3:.0f}" for k in range(9)) +
+              f" wait_ms={ov[0]:.3f} gather_ms={ov[2]:.3f} ar_entry_us={t4[0] / max(t4[3], 1):.0f} ar_work_us={t4[1] / max(t4[3], 1):.0f}",
+              file=sys.stderr, flush=True)
     comm_split = None
     if comm is not None:
         t4 = (C.c_double * 4)()
@@ -447,7 +457,7 @@ def run_prefill(args, env):
         per_kernel = {}
         names = {0: "qkv_gemm", 1: "attention", 2: "out_proj_gemm", 3: "allreduce_ln_1", 4: "ffn_up_gemm", 5: "ffn_down_gemm",
                  6: "allreduce_ln_2", 7: "first_layernorm", 8: "copy_out"}
-        sub_b = B // micro if (world > 1 and micro > 1 and B % micro == 0) else B
+        sub_b = B // micro if (world > 1 and micro > 1 and B % micro == 0 and args.overlap != 2) else B
         for k in range(9):
             if kcnt[k] == 0:
                 continue
@@ -472,9 +482,12 @@ def run_prefill(args, env):
             exposed = {"ms_per_step": comm_ms, "share_of_step": comm_ms / step_ms,
                        "blocked_on_allgather_ms_per_step": ov[0] / ksteps,
                        "allgather_ms_per_step_on_comm_stream": ov[2] / ksteps, "allgathers_per_step": int(ov[3] // ksteps),
-                       "note": "kernel names allreduce_ln_* are the local halves (entry barrier + reduction + residual + LayerNorm "
-                               "on the compute stream); their all-gathers run on the copy engines under the other micro-batch's "
-                               "GEMMs" if args.overlap == 1 and micro > 1 else "all-reduces run in line"}
+                       "note": ("kernel names allreduce_ln_* are the local halves (entry barrier + reduction + residual + LayerNorm "
+                                "on the compute stream); their all-gathers run on the copy engines under the other micro-batch's "
+                                "GEMMs") if args.overlap == 1 and micro > 1 else
+                               ("kernel names allreduce_ln_* are the local halves (entry barrier + reduction + residual + LayerNorm); "
+                                "their all-gathers run as a small copy kernel beside the next GEMM, which waits tile by tile for "
+                                "its rows (that wait is inside the GEMM's time)") if args.overlap == 2 else "all-reduces run in line"}
         line = {
             "metric": "tokens/s", "value": tokens / (ms_total / 1e3), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "p50_latency_ms": p50_ms,
@@ -669,8 +682,9 @@ def main():
     ap.add_argument("--layers", type=int, default=WORKLOAD["layers"], help=argparse.SUPPRESS)
     ap.add_argument("--micro-batches", type=int, default=0,
                     help="micro-requests the batch is split into (0 = default: 2 with more than one GPU)")
-    ap.add_argument("--overlap", type=int, default=1, choices=[0, 1],
-                    help="1: one compute stream + copy-engine all-gathers (default); 0: one stream per micro-request")
+    ap.add_argument("--overlap", type=int, default=1, choices=[0, 1, 2],
+                    help="1: micro-requests on one compute stream + copy-engine all-gathers (default); 0: one stream per "
+                         "micro-request; 2: whole batch, all-gather beside the GEMM that consumes it")
     ap.add_argument("--sweep-max-mb", type=int, default=512, help=argparse.SUPPRESS)
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

@@ -121,6 +121,13 @@ enum liger_epilogue {
  * communicator data region, laid out [world_size][ceil(M/world_size)][N], in the slot of the
  * storing rank.  liger_allreduce_fused(..., one_shot = 3) then finishes the all-reduce from the
  * local slots.  c, ldc are unused.
+ * gather_comm != NULL (any epilogue; the second half of the fusion the reference's unused ReduceScatter / Allgather
+ * wrappers point at, src/layer/func_wrapper.h:45-53): A is the [M, K] tensor that the most recent
+ * liger_allgather_push(gather_comm, gather_channel, ...) is delivering, rank r's rows being
+ * [r*ceil(M/ws), (r+1)*ceil(M/ws)).  The launch does not wait for the gather: every tile's TMA producer waits
+ * (bounded, LIGER_DEV_TIMEOUT on failure) for the row blocks it is about to load, and row tiles are walked in
+ * arrival order, this rank's own rows first, so the transfer runs underneath the contraction.  Issue the
+ * liger_allgather_push call before this one (host order); a, lda must address the gathered tensor itself.
  */
 struct liger_comm;
 typedef struct liger_gemm_args {
@@ -140,6 +147,9 @@ typedef struct liger_gemm_args {
   int kv_stride, kv_pos;        /* LIGER_EPI_QKV_SPLIT only: see above; 0, 0 for plain [B, h, S, D] outputs */
   struct liger_comm* scatter_comm; /* LIGER_EPI_SCATTER only */
   size_t scatter_off;              /* LIGER_EPI_SCATTER only */
+  /* A is being all-gathered: see below.  NULL / 0 for an A operand that is complete. */
+  struct liger_comm* gather_comm;
+  int gather_channel;
 } liger_gemm_args;
 
 LIGER_API int liger_gemm_fp16(const liger_gemm_args* args, void* stream);
@@ -334,6 +344,21 @@ LIGER_API int liger_allreduce_ce(liger_comm* comm, int channel, size_t partial_o
 LIGER_API int liger_allgather_ce(liger_comm* comm, int channel, size_t out_off, int m, int n, int row_begin, int row_end,
                                  void* stream);
 
+/*
+ * All-gather whose consumer is the next GEMM.  Rank r's rows of the [m, n] tensor at out_off go to every peer's
+ * segment, in row blocks of 256 rows, peer by peer (rank-1, rank-2, ...); each delivered (row block, peer) is
+ * announced in the peer's flag line of `ready_channel`.  The data is moved by the copy engines (one peer copy per
+ * row block and peer, followed by a 4-byte copy that publishes the flag), so no SM is taken from the GEMM that
+ * runs beside the transfer.  A GEMM launched with
+ * liger_gemm_args.gather_comm / gather_channel = (comm, ready_channel) starts before the gather has finished and
+ * waits per tile.  A one-warp barrier kernel on `barrier_channel` follows the push, so that anything ordered
+ * after this call on `stream` sees all rows.  Both channels must be used for nothing else while other
+ * collectives are in flight on other streams.  (Nearest reference counterpart: the unused Allgather wrapper,
+ * src/layer/func_wrapper.h:50-53.)
+ */
+LIGER_API int liger_allgather_push(liger_comm* comm, int ready_channel, int barrier_channel, size_t out_off, int m, int n,
+                                   void* stream);
+
 /* ------------------------------------------------------------------------------------------ */
 /* The layer stack and the serving entry points                                               */
 /* ------------------------------------------------------------------------------------------ */
@@ -354,12 +379,14 @@ typedef struct liger_model_config {
   int num_requests;  /* 150 (src/schedule.h:295) */
   int ignore_num;    /* 20 (src/schedule.h:327) */
   int schedule_deep; /* 6 (src/schedule.h:30) */
-  float contention;  /* 0.8 (src/schedule.h:249) */
+  float contention;  /* 0.8 (src/schedule.h:249); 0: the per-direction factors measured by the profile run */
   int poisson;       /* 0: fixed-interval arrivals, 1: exponential gaps */
   int min_seq_len;   /* 16 */
   int seq_round;     /* request lengths are rounded up to a multiple of this (profile bucket) */
   int workspace_slots;
   int kv_capacity;
+  float min_slice_efficiency; /* 0 (reference: any GEMM slice that fits the window, src/init.h:226-259); e.g. 0.7: only
+                                 slices profiled at >= 70 % of the whole kernel's rate */
 } liger_model_config;
 
 LIGER_API void liger_model_config_init(liger_model_config* cfg);
@@ -421,7 +448,11 @@ LIGER_API int liger_model_set_micro_batches(liger_model* model, int micro_batche
  *      (liger_allgather_ce) that runs underneath the other micro-request's next compute segment.  Needs a
  *      communicator with at least 2 * workspace_slots channels; with fewer, mode 0 is used.
  *   0: one stream per micro-request, all-reduces entirely in kernels (liger_allreduce_fused).
- * Both give the bits of the un-split pass.  This is the reference's decomposition + two-stream interleaving
+ *   2: no micro-requests at all: the whole batch on the caller's stream; after the local reduction the all-gather
+ *      (liger_allgather_push, a copy kernel small enough to share the SMs with a GEMM) runs on a second stream
+ *      beside the column-parallel GEMM that consumes it, which starts at once and waits tile by tile for its rows
+ *      (liger_gemm_args.gather_comm).  Needs 3 * workspace_slots channels; with fewer, the modes above apply.
+ * All give the bits of the un-split pass.  This is the reference's decomposition + two-stream interleaving
  * (src/init.h:226-259, src/schedule.h:221-278) re-derived for a GPU whose persistent GEMMs leave no SM resources
  * for a concurrent communication kernel: the decomposition is along the batch, and the overlapped half of the
  * communication uses no SM.

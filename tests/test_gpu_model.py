@@ -123,7 +123,8 @@ def _tp_worker(rank, world, port, case, results):
     cfg = make_cfg(liger, case, slots=4)
     # two flag sets per workspace slot: the pipelined schedule keeps a slot's copy-engine all-gather (communication
     # stream) and its next reduction (compute stream) in flight at the same time
-    comm = Comm(rank, world, lib.liger_model_comm_bytes(C.byref(cfg), world), channels=2 * cfg.workspace_slots)
+    # (three with the gathered schedule, whose all-gather also announces row blocks to the next GEMM)
+    comm = Comm(rank, world, lib.liger_model_comm_bytes(C.byref(cfg), world), channels=3 * cfg.workspace_slots)
     model = C.c_void_p()
     liger.check(lib.liger_model_create(C.byref(model), C.byref(cfg), rank, world, comm.handle))
     x = dev_fill(liger, M, H, 0, 0x10000)
@@ -132,6 +133,22 @@ def _tp_worker(rank, world, port, case, results):
     for rep in range(2):
         liger.check(lib.liger_model_forward(model, ptr(x), ptr(out), c["B"], c["S"], rep % 2, stream_ptr()))
         torch.cuda.synchronize()
+    # the gathered schedule (whole batch; the all-gather runs beside the GEMM that consumes it, which waits tile by
+    # tile for its rows) gives the same bits, pass after pass, with and without per-kernel timing
+    liger.check(lib.liger_model_set_overlap(model, 2))
+    outg = torch.zeros_like(out)
+    for rep in range(3):
+        if rep == 2:
+            liger.check(lib.liger_model_set_kernel_timing(model, 1))
+        outg.zero_()
+        liger.check(lib.liger_model_forward(model, ptr(x), ptr(outg), c["B"], c["S"], rep % 2, stream_ptr()))
+        torch.cuda.synchronize()
+        assert torch.equal(outg, out), f"gathered schedule differs from the in-line pass (rep {rep})"
+    kms0, kcnt0 = (C.c_double * 9)(), (C.c_longlong * 9)()
+    liger.check(lib.liger_model_kernel_times(model, C.byref(kms0), C.byref(kcnt0)))
+    liger.check(lib.liger_model_set_kernel_timing(model, 0))
+    assert kcnt0[0] == c["layer_num"] and kcnt0[4] == c["layer_num"]
+    liger.check(lib.liger_model_set_overlap(model, 1))
     # host-buffer entry point: every rank uploads its rows, rank 0 receives the result
     hin = x.cpu().pin_memory()
     hout = torch.zeros((M, H), dtype=torch.float16).pin_memory()

@@ -153,3 +153,34 @@ def test_bad_configuration_is_rejected(liger):
     cfg = liger.default_config(workspace_slots=2, schedule_deep=6)
     kern = (liger.capi.SimKernel * 1)(liger.capi.SimKernel(GEMM, 1.0))
     assert liger.lib().liger_sim_serve(C.byref(cfg), kern, 1, 1, 1.0, 0.0, None, 0, None, None) == -1
+
+
+def test_measured_contention_factors_replace_the_constant(liger):
+    """contention = 0 asks for the factors a profile run measures (Scheduler::calibrate_contention): the GEMM and
+    the all-reduce are timed alone and side by side.  On a simulated device where kernels running at once do not
+    slow each other down (overlap = 1) the measured factors are exactly 1: the schedule is the one a constant 1.0
+    gives, and it differs from the reference's 0.8.  Where they do slow each other down, by the same amount
+    (overlap = 0.6), the factors stay near 1 -- the window stretches as much as the work in it -- and the
+    schedule again is not the one 0.8 gives."""
+    _, auto, _ = run(liger, liger.capi.MODE_SCHEDULE, rq_interval=100, overlap=1.0, contention=0.0)
+    _, one, _ = run(liger, liger.capi.MODE_SCHEDULE, rq_interval=100, overlap=1.0, contention=1.0)
+    _, ref, _ = run(liger, liger.capi.MODE_SCHEDULE, rq_interval=100, overlap=1.0, contention=0.8)
+    assert auto.secondary_launches == one.secondary_launches and auto.decompositions == one.decompositions
+    assert abs(auto.tokens_per_s - one.tokens_per_s) < 1e-6 * one.tokens_per_s
+    assert (ref.secondary_launches, ref.decompositions) != (one.secondary_launches, one.decompositions)
+    _, auto6, _ = run(liger, liger.capi.MODE_SCHEDULE, rq_interval=100, overlap=0.6, contention=0.0)
+    _, ref6, _ = run(liger, liger.capi.MODE_SCHEDULE, rq_interval=100, overlap=0.6, contention=0.8)
+    assert auto6.secondary_launches > ref6.secondary_launches
+
+
+def test_slices_that_do_not_pay_are_not_used(liger):
+    """A slice of n/factor of a GEMM costs slice_overhead + n/factor of the whole on the simulated device, so every
+    slice runs below the whole kernel's rate, narrow ones far below.  min_slice_efficiency keeps the scheduler from
+    using slices under that fraction of the whole kernel's rate (the reference takes any slice that fits the
+    window, src/init.h:226-259)."""
+    _, anyslice, _ = run(liger, liger.capi.MODE_SCHEDULE, rq_interval=100, slice_overhead=0.05, min_slice_efficiency=0.0)
+    _, lenient, _ = run(liger, liger.capi.MODE_SCHEDULE, rq_interval=100, slice_overhead=0.05, min_slice_efficiency=0.6)
+    _, picky, _ = run(liger, liger.capi.MODE_SCHEDULE, rq_interval=100, slice_overhead=0.05, min_slice_efficiency=0.999)
+    assert anyslice.decompositions > 0
+    assert picky.decompositions == 0          # with any overhead at all no slice reaches 99.9 %
+    assert 0 < lenient.decompositions < anyslice.decompositions
