@@ -192,6 +192,7 @@ class Scheduler {
   // [0.05, 1]) is the factor.  The two factors and the four slow-downs are stored in the Main profile under
   // kernel names 100..105 with batch_size = seq_len = 0, where the reference's reader ignores them.
   static constexpr int kFactorCommUnderComp = 100, kFactorCompUnderComm = 101;
+  static constexpr float kMinOverlapGain = 0.15f;
   void calibrate_contention(int bs, int sq) {
     std::vector<FuncWrap> vec = _model->forward(input, output, bs, sq, 0);
     FuncWrap *g = nullptr, *c = nullptr;
@@ -209,6 +210,7 @@ class Scheduler {
     std::vector<void*> ev_ar(reps_c);
     for (auto& e : ev_ar) e = _rt->create_event();
     float slow[2][2];  // [experiment][0: GEMM, 1: all-reduce]
+    float gain[2];     // how much more work per unit time the pair got done side by side than one after the other
     for (int exp = 0; exp < 2; ++exp) {
       // exp 0: the GEMM is the main segment (stream 0), all-reduces are secondary (stream 1); exp 1: the reverse
       const DynamicNvInitParam& dg = exp == 0 ? DParams0 : DParams1;
@@ -242,19 +244,27 @@ class Scheduler {
       }
       slow[exp][0] = std::max(1.0f, best_g / tg);
       slow[exp][1] = std::max(1.0f, best_c / tc);
+      // work done side by side during the GEMM, in isolated-time units, against the time it took
+      gain[exp] = (tg + (best_g / best_c) * tc) / best_g - 1.0f;
     }
+    // A direction in which running side by side gains less than kMinOverlapGain over running one after the other
+    // is switched off (factor 0: no secondary launches): the schedule's own cost -- a host synchronisation per
+    // segment -- is of that order.  On B200 both directions measure that way at GLM-130B shapes: a persistent GEMM
+    // leaves the all-reduce kernel no registers in two of an SM's four sub-partitions, so the pair serialises.
     auto clamp = [](float v) { return v < 0.05f ? 0.05f : v > 1.0f ? 1.0f : v; };
-    profiling_res_dict[{kFactorCommUnderComp, 0, 0}] = clamp(slow[0][0] / slow[0][1]);
-    profiling_res_dict[{kFactorCompUnderComm, 0, 0}] = clamp(slow[1][1] / slow[1][0]);
+    profiling_res_dict[{kFactorCommUnderComp, 0, 0}] = gain[0] < kMinOverlapGain ? 0.0f : clamp(slow[0][0] / slow[0][1]);
+    profiling_res_dict[{kFactorCompUnderComm, 0, 0}] = gain[1] < kMinOverlapGain ? 0.0f : clamp(slow[1][1] / slow[1][0]);
+    profiling_res_dict[{106, 0, 0}] = gain[0];
+    profiling_res_dict[{107, 0, 0}] = gain[1];
     profiling_res_dict[{102, 0, 0}] = slow[0][0];  // GEMM main, its own slow-down
     profiling_res_dict[{103, 0, 0}] = slow[0][1];  // ... and that of the all-reduces beside it
     profiling_res_dict[{104, 0, 0}] = slow[1][1];  // all-reduce main, its own slow-down
     profiling_res_dict[{105, 0, 0}] = slow[1][0];  // ... and that of the GEMM beside it
     if (SParams.world_rank == 0)
-      printf("Contention factors from measurement: all-reduce under GEMM %.3f (GEMM x%.2f, all-reduce x%.2f); GEMM under "
-             "all-reduce %.3f (all-reduce x%.2f, GEMM x%.2f). \n",
-             profiling_res_dict[{kFactorCommUnderComp, 0, 0}], slow[0][0], slow[0][1],
-             profiling_res_dict[{kFactorCompUnderComm, 0, 0}], slow[1][1], slow[1][0]);
+      printf("Contention factors from measurement (batch %d, seq %d): all-reduce under GEMM %.3f (GEMM x%.2f, all-reduce x%.2f, "
+             "gain %.0f %%); GEMM under all-reduce %.3f (all-reduce x%.2f, GEMM x%.2f, gain %.0f %%). \n", bs, sq,
+             profiling_res_dict[{kFactorCommUnderComp, 0, 0}], slow[0][0], slow[0][1], 100.0f * gain[0],
+             profiling_res_dict[{kFactorCompUnderComm, 0, 0}], slow[1][1], slow[1][0], 100.0f * gain[1]);
   }
   // The factor of a window whose main segment is of class `main_type`: the configured constant, or, with
   // BertInitParam::contention == 0, the measured one (0.8 where the profile holds none).
@@ -369,6 +379,12 @@ class Scheduler {
 
   // ---- Liger: interleaved two-stream schedule (src/schedule.h:221-278) ---------------------------------
   void run_stream_sync() {
+    // measured factors that switch both directions off: on this machine the derived schedule is the unscheduled one
+    if (BertParams.contention <= 0.0f && contention_factor(COMMUNICATION) <= 0.0f && contention_factor(GEMM) <= 0.0f) {
+      if (SParams.world_rank == 0) printf("Interleaving is switched off by the measured contention factors. \n");
+      run_sequential();
+      return;
+    }
     tag = true;
     _t0 = _rt->wall_seconds();
     float time_planned = 0.0f;

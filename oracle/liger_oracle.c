@@ -5,13 +5,16 @@
  * path.  Only tests/, __graft_entry__.smoke() and bench.py's CPU-baseline legs may build, load
  * or call this file; the product library never links or calls it.
  *
- * PARITY UNPINNED: the reference ships no golden vectors, known-answer tests or CPU path for
- * this arithmetic (src/test_model.h is timing-only; weights and inputs are never initialised,
- * outputs never read back).  Its dense contractions and reductions live in cuBLAS
- * (cublasGemmEx / cublasGemmStridedBatchedEx, call sites src/layer/func_wrapper.h:25,35) and
- * NCCL (ncclAllReduce, src/layer/func_wrapper.h:42), closed libraries that are not part of the
- * reference tree.  Each function below therefore follows the reference's own call sites and
- * CUDA kernels, cited per function, and computes in plain fp32.
+ * PARITY PINNED TO THE REFERENCE'S OWN OUTPUT.  The reference ships no golden vectors, known-answer tests or CPU
+ * path for this arithmetic (src/test_model.h is timing-only; weights and inputs are never initialised, outputs
+ * never read back), and its dense contractions and reductions live in cuBLAS (cublasGemmEx /
+ * cublasGemmStridedBatchedEx, call sites src/layer/func_wrapper.h:25,35) and NCCL (ncclAllReduce,
+ * src/layer/func_wrapper.h:42), closed libraries outside the reference tree.  So the reference itself is run: its
+ * unmodified sources, compiled with a harness (oracle/ref_harness/) into oracle/_ref/, execute each of its kernels
+ * and its whole layer stack on seeded inputs on the GPU, and tests/test_reference_parity.py compares those outputs
+ * with the functions below (per operator within 1e-2, data movement bit for bit; whole stacks within 2e-2, the
+ * reference accumulating its GEMMs in fp16).  Each function follows the reference's call sites and CUDA kernels,
+ * cited per function, and computes in plain fp32.
  *
  * Conventions: every tensor is a dense row-major float array whose values are fp16
  * representable on entry.  Weights use the reference orientation W[k][n] with Y = X * W
