@@ -118,6 +118,7 @@ SIGNATURES = {
     "liger_model_kernel_work": (_I, [_P, _I, _I, _I, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "liger_serve": (_I, [_P, _I, BCAST_INT_FN, BARRIER_FN, _P, C.c_char_p, _I, C.POINTER(ServingMetrics)]),
     "liger_profile_rewrite": (_I, [C.c_char_p, C.c_char_p, _I, C.POINTER(_I), C.POINTER(C.c_double)]),
+    "liger_profile_predict": (_I, [C.c_char_p, _I, _I, _I, _I, _I, C.POINTER(C.c_double)]),
     "liger_sim_serve": (_I, [C.POINTER(ModelConfig), C.POINTER(SimKernel), _I, _I, C.c_double, C.c_double,
                              C.POINTER(SimLaunch), _I, C.POINTER(_I), C.POINTER(ServingMetrics)]),
     "liger_sim_serve_rank": (_I, [C.POINTER(ModelConfig), C.POINTER(SimKernel), _I, _I, C.c_double, C.c_double, _I, _I,

@@ -100,7 +100,7 @@ allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t recv_o
                        const __half* __restrict__ beta, int n, int row_lo, int row_hi, int one_shot, int rows_per_rank,
                        uint32_t epoch_in,
                        uint32_t epoch_out, unsigned int* done_counter, unsigned long long* stamps, DeviceStatus* st,
-                       int barrier_mode) {  // 0: exit barrier only (entry ran as its own kernel); 1: no exit barrier; 2: entry barrier here too
+                       int barrier_mode) {  // 0: exit barrier only (entry ran as its own kernel); 1: no exit barrier; 2: entry barrier here too; 3: entry here, no exit
   __shared__ float red[32];
   __shared__ int s_fail;
   __shared__ int s_last;
@@ -111,7 +111,7 @@ allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t recv_o
   // one-shot form (barrier_mode == 2) does it here instead and saves a launch: block 0 publishes this rank's
   // arrival, every block waits for all ranks' arrivals on its own (nothing else is running beside a decode step, so
   // blocks that spin take nothing from anyone).
-  if (barrier_mode == 2) {
+  if (barrier_mode >= 2) {
     const unsigned long long t_enter = globaltimer_ns();
     if (blockIdx.x == 0) barrier_signal(c, channel, epoch_in);
     barrier_wait(c, channel, epoch_in, &s_fail, st, 0x200u);
@@ -295,7 +295,7 @@ allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t recv_o
     if (ticket == gridDim.x - 1) { *done_counter = 0u; s_last = 1; }
   }
   __syncthreads();
-  if (s_last && barrier_mode == 1) {
+  if (s_last && (barrier_mode == 1 || barrier_mode == 3)) {
     if (threadIdx.x == 0) { stamps[2] = globaltimer_ns(); stamps[5] += stamps[2] - stamps[1]; stamps[7] += 1ull; }
   } else if (s_last) {
     const unsigned long long t_work = globaltimer_ns();
@@ -483,8 +483,12 @@ extern "C" int liger_allreduce_fused(liger_comm* c, int channel, size_t partial_
   CommDev cd;
   for (int p = 0; p < kMaxRanks; ++p) cd.base[p] = p < c->ws ? c->peer[p] : nullptr;
   cd.rank = c->rank; cd.ws = c->ws;
-  if (one_shot < 0 || one_shot > 5 || one_shot == 4)
-    return set_error(LIGER_ERR_INVALID, "allreduce_fused: one_shot must be 0, 1, 2, 3 or 5");
+  if (one_shot < 0 || one_shot > 6 || one_shot == 4)
+    return set_error(LIGER_ERR_INVALID, "allreduce_fused: one_shot must be 0, 1, 2, 3, 5 or 6");
+  // 6 = one-shot without the exit barrier: the caller alternates between two partial buffers, so the barrier at the
+  // entry of the next call on this channel is what tells it that every rank has finished reading this one's input
+  const int barrier_mode = one_shot == 5 ? 1 : one_shot == 1 ? 2 : one_shot == 6 ? 3 : 0;
+  if (one_shot == 6) one_shot = 1;
   int lo = row_begin, hi = row_end;
   if (one_shot != 1) {
     const int rpr = (m + c->ws - 1) / c->ws;
@@ -512,7 +516,7 @@ extern "C" int liger_allreduce_fused(liger_comm* c, int channel, size_t partial_
   if (grid > cap) grid = cap;
   if (grid < 1) grid = 1;
   const uint32_t e_in = ++c->epoch[channel];
-  const uint32_t e_out = one_shot == 5 ? e_in : ++c->epoch[channel];  // mode 5 has no exit barrier
+  const uint32_t e_out = (barrier_mode == 1 || barrier_mode == 3) ? e_in : ++c->epoch[channel];  // no exit barrier: no second epoch
   int rc;
   if (one_shot != 1) {
     allreduce_entry_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(cd, channel, e_in, c->stamps + 8 * channel,
@@ -522,7 +526,7 @@ extern "C" int liger_allreduce_fused(liger_comm* c, int channel, size_t partial_
   launch_allreduce_kernel(
       grid, (cudaStream_t)stream, n, cd, channel, kFlagRegionBytes + partial_off, (size_t)0, kFlagRegionBytes + out_off, (const __half*)residual_in, (__half*)hidden, (const __half*)bias,
       (const __half*)gamma, (const __half*)beta, n, lo, hi, one_shot, rpr_all, e_in, e_out, c->done + channel,
-      c->stamps + 8 * channel, dev->status_dev, one_shot == 5 ? 1 : one_shot == 1 ? 2 : 0);
+      c->stamps + 8 * channel, dev->status_dev, barrier_mode);
   return check_launch("allreduce_fused_kernel");
 }
 

@@ -814,6 +814,7 @@ extern "C" int liger_serve(liger_model* m, int mode, liger_bcast_int_fn bcast, l
       wsq = std::max(step, wsq / step * step);
       if (wb != m->bp.max_batch_size) scheduler.profile(wb, wb + 1, wsq, wsq + 1, main_f, sub_f, 1);
       scheduler.profile(m->bp.max_batch_size, m->bp.max_batch_size + 1, 1, m->bp.max_seq_len + 1, main_f, sub_f, step);
+      policy_trial(m->model, m->bp, m->sp, m->io_in, m->io_out, &rt, &coord, main_f, sub_f);
       return LIGER_OK;
     }
     scheduler.load_profiles(main_f, sub_f);
@@ -855,6 +856,19 @@ extern "C" int liger_profile_rewrite(const char* in_path, const char* out_path, 
     return LIGER_OK;
   } catch (const std::exception& e) {
     return liger::set_error(LIGER_ERR_INVALID, "profile_rewrite: %s", e.what());
+  }
+}
+
+extern "C" int liger_profile_predict(const char* main_path, int max_batch, int max_seq, int name, int batch, int seq_len,
+                                     double* duration_ms) {
+  if (!main_path || !duration_ms || max_batch < 1 || max_seq < 1 || batch < 1 || seq_len < 1)
+    return liger::set_error(LIGER_ERR_INVALID, "profile_predict: bad argument");
+  try {
+    MainDict d = MainFileToDict(main_path);
+    *duration_ms = predict_duration(d, name, batch, seq_len, max_batch, max_seq);
+    return LIGER_OK;
+  } catch (const std::exception& e) {
+    return liger::set_error(LIGER_ERR_INVALID, "profile_predict: %s", e.what());
   }
 }
 

@@ -167,6 +167,9 @@ struct Workspace {
   half_t* act = nullptr;      // [M, F/ws]
   float* decode_scratch = nullptr;
   size_t partial_off = 0, normed_off = 0, xbuf_off = 0, recv_off = 0;  // byte offsets inside the comm data region
+  // decode: the two all-reduces of a layer read their partials from two different buffers in turn (`partial` and
+  // the receive region), which lets the latency-bound one-shot all-reduce drop its exit barrier (mode 6)
+  bool alternating_partials = false;
 };
 
 // What follows an all-reduce (or, with world_size == 1, the row-parallel GEMM): an optional
@@ -291,7 +294,7 @@ class Bert_MHA {
       COMM_ARGS c;
       c.comm = sp.comm; c.channel = sh.slot; c.partial_off = w.partial_off; c.out_off = post.out_off;
       c.m = M; c.n = n; c.row_begin = 0; c.row_end = M;
-      c.one_shot = is_one_shot(M, n) ? 1 : 3;
+      c.one_shot = is_one_shot(M, n) ? (w.alternating_partials ? 6 : 1) : 3;
       if (!is_one_shot(M, n) && use_copy_engines()) { c.copy_engine = 1; c.recv_off = w.recv_off; }
       if (post.residual_in) { c.residual_in = post.residual_in; c.hidden = w.hidden; c.bias = post.bias; }
       c.gamma = post.gamma; c.beta = post.beta;
@@ -530,10 +533,17 @@ class Bert_Model {
         mlp_post.out = w.xbuf; mlp_post.out_off = w.xbuf_off;
         if (ws == 1) mlp_post.direct_out = output;
       }
-      std::vector<FuncWrap> t = e->MHA->forward_decode(w.normed, w, mha_post, sh, e->k_cache, e->v_cache, kv_len,
+      // attention block: partials in `partial`; MLP block: partials in the receive region (unused by the one-shot path)
+      Workspace wa = w, wb = w;
+      if (ws > 1 && Bert_MHA::is_one_shot(M, H)) {
+        wa.alternating_partials = wb.alternating_partials = true;
+        wb.partial = (half_t*)((uint8_t*)liger_comm_data(SParam.comm) + w.recv_off);
+        wb.partial_off = w.recv_off;
+      }
+      std::vector<FuncWrap> t = e->MHA->forward_decode(w.normed, wa, mha_post, sh, e->k_cache, e->v_cache, kv_len,
                                                        BertParams.kv_capacity);
       vec.insert(vec.end(), t.begin(), t.end());
-      t = e->MLP->forward(w.normed, w, mlp_post, sh);
+      t = e->MLP->forward(w.normed, wb, mlp_post, sh);
       vec.insert(vec.end(), t.begin(), t.end());
       resid = w.hidden;
     }

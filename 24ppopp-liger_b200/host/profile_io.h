@@ -176,4 +176,36 @@ inline SubDict SubTextToDict(const std::string& text) {
 inline MainDict MainFileToDict(const std::string& filename) { return MainTextToDict(read_text_file(filename)); }
 inline SubDict SubFileToDict(const std::string& filename) { return SubTextToDict(read_text_file(filename)); }
 
+
+// The cost model behind Scheduler::lookup_duration (see there): exact key, else linear interpolation between the
+// nearest profiled lengths of the same batch size, proportional extrapolation beyond the last one, the nearest
+// profiled batch size scaled by tokens otherwise; 0 when the kernel was never profiled.
+inline float predict_duration(const MainDict& dict, int name, int bs, int sq, int max_bs, int max_sq) {
+  auto it = dict.find({name, bs, sq});
+  if (it != dict.end()) return it->second;
+  int lo = 0, hi = 0;
+  float dlo = 0.0f, dhi = 0.0f;
+  for (int s = sq - 1; s >= 1; --s) {
+    it = dict.find({name, bs, s});
+    if (it != dict.end()) { lo = s; dlo = it->second; break; }
+  }
+  for (int s = sq + 1; s <= max_sq; ++s) {
+    it = dict.find({name, bs, s});
+    if (it != dict.end()) { hi = s; dhi = it->second; break; }
+  }
+  if (lo && hi) return dlo + (dhi - dlo) * (float)(sq - lo) / (float)(hi - lo);
+  if (hi) return dhi;  // shorter than anything profiled: a floor, not a line through 0
+  if (lo) return dlo * (float)sq / (float)lo;
+  for (int d = 1; d <= max_bs; ++d) {
+    const int cand[2] = {bs + d, bs - d};
+    for (int b : cand) {
+      if (b < 1 || b > max_bs) continue;
+      bool any = false;
+      for (int s = 1; s <= max_sq && !any; ++s) any = dict.count({name, b, s}) != 0;
+      if (any) return predict_duration(dict, name, b, sq, max_bs, max_sq) * (float)bs / (float)b;
+    }
+  }
+  return 0.0f;
+}
+
 }  // namespace liger_host

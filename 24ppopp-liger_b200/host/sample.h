@@ -208,13 +208,31 @@ class Sample {
 
   // Try to split the GEMM at the cursor so that its first part fits `time_planned`
   // (src/init.h:226-259): the largest i+1 of `factor` slices whose profiled time vec[i] fits.
+  // Slice durations of kernel `name` at this request's shape: the profiled vector, or, for a length between
+  // profiled ones, the vector of the next profiled length of the same batch size scaled by the ratio of the whole
+  // kernel's (interpolated) duration to the largest profiled slice.
+  bool slice_durations(int name, float whole_duration, std::vector<float>& out) const {
+    auto it = profiling_decompse_res_dict->find({name, batch_size, seq_len});
+    if (it != profiling_decompse_res_dict->end()) { out = it->second; return (int)out.size() >= _factor - 1; }
+    for (int s = seq_len + 1; s <= seq_len + 4096; ++s) {
+      it = profiling_decompse_res_dict->find({name, batch_size, s});
+      if (it == profiling_decompse_res_dict->end()) continue;
+      if ((int)it->second.size() < _factor - 1 || it->second.back() <= 0.0f) return false;
+      out = it->second;
+      // the (factor-1)/factor slice of the borrowed shape against the same share of this shape's whole kernel
+      const float scale = whole_duration > 0.0f ? whole_duration * (float)(_factor - 1) / (float)_factor / out.back() : 1.0f;
+      if (scale < 1.0f) for (float& v : out) v *= scale;
+      return true;
+    }
+    return false;
+  }
+
   bool possible_duration(float time_planned) {
     if (_factor < 2 || profiling_decompse_res_dict == nullptr) return false;
     if (_sub_empty()) {
       const FuncWrap& whole = FuncWrapVec.at(exe_num);
-      auto it = profiling_decompse_res_dict->find({whole.name, batch_size, seq_len});
-      if (it == profiling_decompse_res_dict->end() || (int)it->second.size() < _factor - 1) return false;
-      const std::vector<float>& vec = it->second;
+      std::vector<float> vec;
+      if (!slice_durations(whole.name, whole.duration, vec)) return false;
       _whole_duration = whole.duration;
       for (int i = _factor - 2; i >= 0; --i) {
         if (time_planned >= vec[i] && slice_pays(i + 1, vec[i])) {
@@ -231,9 +249,8 @@ class Sample {
     // a remainder is pending: split it again
     const FuncWrap pending = _SubFuncWrapVec.at(_sub_exe_num);
     if (_sub_exe_num + 1 != _SubFuncWrapVec.size()) return false;  // only the trailing remainder re-splits
-    auto it = profiling_decompse_res_dict->find({pending.name, batch_size, seq_len});
-    if (it == profiling_decompse_res_dict->end() || (int)it->second.size() < _factor - 1) return false;
-    const std::vector<float>& vec = it->second;
+    std::vector<float> vec;
+    if (!slice_durations(pending.name, _whole_duration, vec)) return false;
     for (int i = _remain - 2; i >= 0; --i) {
       if (time_planned >= vec[i] && slice_pays(i + 1, vec[i])) {
         const int n_run = i + 1;

@@ -290,15 +290,14 @@ class Scheduler {
     return time_min / (float)itr;
   }
 
-  // profiled duration of kernel `name` for (bs, sq); falls back to the next profiled length >= sq
+  // Cost model: profiled duration of kernel `name` for (bs, sq).  The reference looks the exact key up and gets 0 for
+  // anything it did not profile (operator[] default, src/schedule.h:166), which is why it profiles every integer
+  // length (src/test_schedule.h:103).  Here a profile taken at a few lengths serves all of them: between two profiled
+  // lengths of the same batch size the duration is interpolated linearly, beyond the last one it is extrapolated in
+  // proportion to the length, and a batch size that was not profiled borrows the nearest profiled one scaled by the
+  // token count.
   float lookup_duration(int name, int bs, int sq) const {
-    auto it = profiling_res_dict.find({name, bs, sq});
-    if (it != profiling_res_dict.end()) return it->second;
-    for (int s = sq + 1; s <= BertParams.max_seq_len; ++s) {
-      it = profiling_res_dict.find({name, bs, s});
-      if (it != profiling_res_dict.end()) return it->second;
-    }
-    return 0.0f;  // the reference's operator[] default (src/schedule.h:166)
+    return predict_duration(profiling_res_dict, name, bs, sq, BertParams.max_batch_size, BertParams.max_seq_len);
   }
 
   // ---- admission (src/schedule.h:159-202) --------------------------------------------------------
@@ -378,10 +377,22 @@ class Scheduler {
   }
 
   // ---- Liger: interleaved two-stream schedule (src/schedule.h:221-278) ---------------------------------
+  // With measured constants (contention == 0) the profile also holds the outcome of a trial that test_profile runs on
+  // the machine: a saturated burst of requests through this loop and through run_sequential (kernel name
+  // kTrialRatio: tokens/s of the interleaved loop over tokens/s of the unscheduled one).  Where interleaving did not
+  // win that trial -- or both measured factors are 0 -- the derived schedule IS the unscheduled one.
+  static constexpr int kTrialRatio = 108;
+  bool force_interleave = false;  // set by the trial itself
+  bool interleaving_pays() const {
+    if (BertParams.contention > 0.0f || force_interleave) return true;
+    if (contention_factor(COMMUNICATION) <= 0.0f && contention_factor(GEMM) <= 0.0f) return false;
+    auto it = profiling_res_dict.find({kTrialRatio, 0, 0});
+    return it == profiling_res_dict.end() || it->second > 1.02f;
+  }
+
   void run_stream_sync() {
-    // measured factors that switch both directions off: on this machine the derived schedule is the unscheduled one
-    if (BertParams.contention <= 0.0f && contention_factor(COMMUNICATION) <= 0.0f && contention_factor(GEMM) <= 0.0f) {
-      if (SParams.world_rank == 0) printf("Interleaving is switched off by the measured contention factors. \n");
+    if (!interleaving_pays()) {
+      if (SParams.world_rank == 0) printf("Interleaving did not pay in the profile's trial on this machine: unscheduled loop. \n");
       run_sequential();
       return;
     }

@@ -310,6 +310,9 @@ LIGER_API int liger_comm_timing(liger_comm* comm, int channel, int reset, double
  * partial are taken as they are (no sum over peers) and stored to every rank.
  * one_shot == 5: input as for 3, but the finished rows are stored into this rank's own segment only and there is no
  * exit barrier -- the first half of a split collective whose second half is liger_allgather_ce on another stream.
+ * one_shot == 6: as 1, without the exit barrier.  Safe only if consecutive calls on the channel read their partials
+ * from two alternating buffers: the entry barrier of call k+1 then tells every rank that all ranks have finished
+ * reading the input of call k, before anything rewrites it for call k+2 (a decode step's two all-reduces per layer).
  * Waits on peers are bounded; on timeout the device status word is set.
  * N % 8 == 0, N <= 16384.  row_begin / row_end allow the collective to be issued in slices
  * (decompose_comm_callback, src/utils.h:262-281).
@@ -543,6 +546,16 @@ LIGER_API int liger_serve(liger_model* model, int mode, liger_bcast_int_fn bcast
  * LIGER_ERR_INVALID with the parse position in liger_last_error().  out_path may be NULL.
  */
 LIGER_API int liger_profile_rewrite(const char* in_path, const char* out_path, int is_sub, int* entries, double* duration_sum);
+/*
+ * What the scheduler's cost model predicts for kernel `name` of a (batch, seq_len) request, from the Main profile at
+ * main_path taken for a model of (max_batch, max_seq): the profiled value where there is one; otherwise linear
+ * interpolation between the nearest profiled lengths of the same batch size, extrapolation in proportion to the length
+ * beyond the last one, and the nearest profiled batch size scaled by the token count.  The reference looks the exact
+ * key up and uses 0 for everything else (src/schedule.h:166), hence its profile over every integer length
+ * (src/test_schedule.h:103).
+ */
+LIGER_API int liger_profile_predict(const char* main_path, int max_batch, int max_seq, int name, int batch, int seq_len,
+                                    double* duration_ms);
 
 /*
  * The scheduling logic on a simulated device (no GPU): a layer is given as kernels_per_layer

@@ -281,6 +281,15 @@ def _decode_tp_worker(rank, world, port, results):
     dist.barrier()
     liger.check(lib.liger_model_decode(model, ptr(x), ptr(out), B, kv_len, 0, stream_ptr()))
     torch.cuda.synchronize()
+    # the same step again, eight times back to back without host synchronisation: it appends the same K / V at the
+    # same position, so every repetition must give the same bits (the one-shot all-reduces of consecutive steps reuse
+    # their two partial buffers in turn and have no exit barrier)
+    outs = [torch.zeros_like(out) for _ in range(8)]
+    for o in outs:
+        liger.check(lib.liger_model_decode(model, ptr(x), ptr(o), B, kv_len, 0, stream_ptr()))
+    torch.cuda.synchronize()
+    for o in outs:
+        assert torch.equal(o, out)
     st = (C.c_uint * 4)()
     assert lib.liger_device_status(C.byref(st)) == 0, list(st)
     results[rank] = to_np(out)

@@ -115,3 +115,28 @@ def test_empty_profile_is_valid(liger, tmp_path):
 
 def test_missing_profile_file_is_an_error(liger):
     assert liger.lib().liger_profile_rewrite(b"/nonexistent/Main.json", None, 0, None, None) == -1
+
+
+def test_cost_model_interpolates_between_profiled_shapes(liger, tmp_path):
+    """The scheduler's cost model (liger_profile_predict) serves every (batch, length) from a profile taken at a few
+    lengths; the reference's lookup returns 0 for anything it did not profile (src/schedule.h:166)."""
+    lib = liger.lib()
+    main = [{"kernel_name": 4, "batch_size": 8, "seq_len": s, "duration": 0.2 + s * 0.01} for s in (128, 256, 512)]
+    main += [{"kernel_name": 100, "batch_size": 0, "seq_len": 0, "duration": 0.06}]      # a measured contention factor
+    p = tmp_path / "Main.json"
+    p.write_text(json.dumps(main))
+
+    def predict(name, bs, sq):
+        out = C.c_double(-1.0)
+        liger.check(lib.liger_profile_predict(str(p).encode(), 16, 1024, name, bs, sq, C.byref(out)))
+        return out.value
+
+    assert predict(4, 8, 256) == pytest.approx(0.2 + 2.56, rel=1e-6)                    # profiled
+    assert predict(4, 8, 192) == pytest.approx(0.2 + 1.92, rel=1e-6)                    # between 128 and 256: linear
+    assert predict(4, 8, 300) == pytest.approx(0.2 + 3.00, rel=1e-6)
+    assert predict(4, 8, 64) == pytest.approx(0.2 + 1.28, rel=1e-6)                     # below the first: its value, a floor
+    assert predict(4, 8, 1024) == pytest.approx((0.2 + 5.12) * 2.0, rel=1e-6)           # beyond the last: in proportion
+    assert predict(4, 4, 256) == pytest.approx((0.2 + 2.56) * 0.5, rel=1e-6)            # other batch size: by tokens
+    assert predict(4, 16, 192) == pytest.approx((0.2 + 1.92) * 2.0, rel=1e-6)
+    assert predict(5, 8, 256) == 0.0                                                    # never profiled
+    assert lib.liger_profile_predict(None, 16, 1024, 4, 8, 256, None) == -1
