@@ -232,7 +232,7 @@ constexpr int kDecChunk = 256;  // keys per CTA
 __host__ __device__ inline int decode_splits(int kv_len) { return (kv_len + kDecChunk - 1) / kDecChunk; }
 
 // partial layout per (b, head, split): [m, l, acc[D]] floats
-template <int D>
+template <int D, int U>
 __global__ void __launch_bounds__(kDecThreads)
 attention_decode_partial_kernel(const __half* __restrict__ q, const __half* __restrict__ kc, const __half* __restrict__ vc,
                                 float* __restrict__ scratch, int heads, int kv_len, int kv_stride, float scale) {
@@ -264,36 +264,65 @@ attention_decode_partial_kernel(const __half* __restrict__ q, const __half* __re
   float m = -INFINITY, l = 0.0f, acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   const int k_begin = split * kDecChunk;
   const int k_end = min(kv_len, k_begin + kDecChunk);
-  // every lane of a warp runs the same number of steps (the shuffles need the full warp); a
-  // sub-group whose key falls past the end of the chunk just skips the update
-  for (int base = k_begin + warp * KPW; base < k_end; base += (kDecThreads / 32) * KPW) {
-    const int key = base + sub;
-    const bool valid = key < k_end;
-    uint4 ku = make_uint4(0, 0, 0, 0), vu = make_uint4(0, 0, 0, 0);
-    if (valid) {
-      ku = __ldg(reinterpret_cast<const uint4*>(kbase + (size_t)key * D + li * 8));
-      vu = __ldg(reinterpret_cast<const uint4*>(vbase + (size_t)key * D + li * 8));
-    }
-    const __half2* kh = reinterpret_cast<const __half2*>(&ku);
-    float dot = 0.0f;
+  // Every lane of a warp runs the same number of steps (the shuffles need the full warp).  A step
+  // fetches U keys and values per lane group before it uses any of them -- U x 32 bytes in flight per
+  // thread is what keeps HBM busy -- and folds them into the running state with one rescale.
+  constexpr int STEP = (kDecThreads / 32) * KPW;  // keys the CTA covers per unrolled slot
+  for (int base = k_begin + warp * KPW; base < k_end; base += STEP * U) {
+    uint4 ku[U], vu[U];
+    bool valid[U];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float2 f = __half22float2(kh[j]);
-      dot += qv[2 * j] * f.x + qv[2 * j + 1] * f.y;
+    for (int u = 0; u < U; ++u) {
+      const int key = base + u * STEP + sub;
+      valid[u] = key < k_end;
+      ku[u] = make_uint4(0, 0, 0, 0);
+      vu[u] = make_uint4(0, 0, 0, 0);
+      if (valid[u]) {
+        ku[u] = __ldcs(reinterpret_cast<const uint4*>(kbase + (size_t)key * D + li * 8));
+        vu[u] = __ldcs(reinterpret_cast<const uint4*>(vbase + (size_t)key * D + li * 8));
+      }
     }
+    float dot[U];
 #pragma unroll
-    for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-    if (valid) {
-      const float m_new = fmaxf(m, dot);
-      const float alpha = __expf(m - m_new);
-      const float p = __expf(dot - m_new);
-      l = l * alpha + p;
-      const __half2* vh = reinterpret_cast<const __half2*>(&vu);
+    for (int u = 0; u < U; ++u) {
+      const __half2* kh = reinterpret_cast<const __half2*>(&ku[u]);
+      float d = 0.0f;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        float2 f = __half22float2(vh[j]);
-        acc[2 * j] = acc[2 * j] * alpha + p * f.x;
-        acc[2 * j + 1] = acc[2 * j + 1] * alpha + p * f.y;
+        float2 f = __half22float2(kh[j]);
+        d += qv[2 * j] * f.x + qv[2 * j + 1] * f.y;
+      }
+      dot[u] = d;
+    }
+#pragma unroll
+    for (int o = LPK / 2; o > 0; o >>= 1) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) dot[u] += __shfl_xor_sync(0xffffffffu, dot[u], o);
+    }
+    float m_new = m;
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (valid[u]) m_new = fmaxf(m_new, dot[u]);
+    if (m_new != -INFINITY) {  // false only while this lane group has seen no key at all
+      const float alpha = (m == -INFINITY) ? 0.0f : __expf(m - m_new);
+      float pr[U], psum = 0.0f;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        pr[u] = valid[u] ? __expf(dot[u] - m_new) : 0.0f;
+        psum += pr[u];
+      }
+      l = l * alpha + psum;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] *= alpha;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const __half2* vh = reinterpret_cast<const __half2*>(&vu[u]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 f = __half22float2(vh[j]);
+          acc[2 * j] += pr[u] * f.x;
+          acc[2 * j + 1] += pr[u] * f.y;
+        }
       }
       m = m_new;
     }
@@ -338,6 +367,28 @@ __global__ void attention_decode_merge_kernel(const float* __restrict__ scratch,
     a += src[(size_t)s * (D + 2) + 2 + d] * sc;
   }
   out[(size_t)b * ldo + head * D + d] = __float2half_rn(a / (ll + 1e-6f));
+}
+
+// Keys each lane group fetches before it uses them (LIGER_DEC_UNROLL = 1, 2, 4 or 8 overrides the default).
+static int decode_unroll() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("LIGER_DEC_UNROLL");
+    const int u = e ? atoi(e) : 4;
+    v = (u == 1 || u == 2 || u == 4 || u == 8) ? u : 4;
+  }
+  return v;
+}
+
+template <int D>
+static void launch_decode_partial(dim3 grid, cudaStream_t s, const __half* q, const __half* kc, const __half* vc, float* scratch,
+                                  int heads, int kv_len, int kv_stride, float scale) {
+  switch (decode_unroll()) {
+    case 1: attention_decode_partial_kernel<D, 1><<<grid, kDecThreads, 0, s>>>(q, kc, vc, scratch, heads, kv_len, kv_stride, scale); break;
+    case 2: attention_decode_partial_kernel<D, 2><<<grid, kDecThreads, 0, s>>>(q, kc, vc, scratch, heads, kv_len, kv_stride, scale); break;
+    case 8: attention_decode_partial_kernel<D, 8><<<grid, kDecThreads, 0, s>>>(q, kc, vc, scratch, heads, kv_len, kv_stride, scale); break;
+    default: attention_decode_partial_kernel<D, 4><<<grid, kDecThreads, 0, s>>>(q, kc, vc, scratch, heads, kv_len, kv_stride, scale); break;
+  }
 }
 
 // attention_sm100.cu: the tcgen05 kernel (head_dim 128, no mask tensor)
@@ -407,16 +458,14 @@ extern "C" int liger_attention_decode(const void* q, const void* k_cache, const 
   const int ns = decode_splits(kv_len);
   dim3 grid(ns, heads, batch), mgrid(heads, batch);
   if (head_dim == 128) {
-    attention_decode_partial_kernel<128><<<grid, kDecThreads, 0, s>>>((const __half*)q, (const __half*)k_cache,
-                                                                      (const __half*)v_cache, (float*)scratch, heads,
-                                                                      kv_len, kv_stride, scale);
+    launch_decode_partial<128>(grid, s, (const __half*)q, (const __half*)k_cache, (const __half*)v_cache, (float*)scratch, heads, kv_len,
+                               kv_stride, scale);
     int rc = check_launch("attention_decode_partial_kernel");
     if (rc != LIGER_OK) return rc;
     attention_decode_merge_kernel<128><<<mgrid, 128, 0, s>>>((const float*)scratch, (__half*)out, heads, ns, ldo);
   } else if (head_dim == 64) {
-    attention_decode_partial_kernel<64><<<grid, kDecThreads, 0, s>>>((const __half*)q, (const __half*)k_cache,
-                                                                     (const __half*)v_cache, (float*)scratch, heads,
-                                                                     kv_len, kv_stride, scale);
+    launch_decode_partial<64>(grid, s, (const __half*)q, (const __half*)k_cache, (const __half*)v_cache, (float*)scratch, heads, kv_len,
+                               kv_stride, scale);
     int rc = check_launch("attention_decode_partial_kernel");
     if (rc != LIGER_OK) return rc;
     attention_decode_merge_kernel<64><<<mgrid, 64, 0, s>>>((const float*)scratch, (__half*)out, heads, ns, ldo);
@@ -493,15 +542,13 @@ extern "C" int liger_attention_decode_noalloc(const void* q, const void* k_cache
   // every partial that the merge kernel reads is written by the partial kernel of the same call, so
   // nothing left over from an earlier call is ever consumed and nothing needs clearing
   if (head_dim == 128) {
-    attention_decode_partial_kernel<128><<<grid, kDecThreads, 0, s>>>((const __half*)q, (const __half*)k_cache,
-                                                                      (const __half*)v_cache, scratch, heads, kv_len,
-                                                                      kv_stride, scale);
+    launch_decode_partial<128>(grid, s, (const __half*)q, (const __half*)k_cache, (const __half*)v_cache, scratch, heads, kv_len,
+                               kv_stride, scale);
     if ((rc = check_launch("attention_decode_partial_kernel")) != LIGER_OK) return rc;
     attention_decode_merge_kernel<128><<<mgrid, 128, 0, s>>>(scratch, (__half*)out, heads, ns, ldo);
   } else {
-    attention_decode_partial_kernel<64><<<grid, kDecThreads, 0, s>>>((const __half*)q, (const __half*)k_cache,
-                                                                     (const __half*)v_cache, scratch, heads, kv_len,
-                                                                     kv_stride, scale);
+    launch_decode_partial<64>(grid, s, (const __half*)q, (const __half*)k_cache, (const __half*)v_cache, scratch, heads, kv_len,
+                               kv_stride, scale);
     if ((rc = check_launch("attention_decode_partial_kernel")) != LIGER_OK) return rc;
     attention_decode_merge_kernel<64><<<mgrid, 64, 0, s>>>(scratch, (__half*)out, heads, ns, ldo);
   }

@@ -560,7 +560,10 @@ extern "C" int liger_model_decode(liger_model* m, const void* input, void* outpu
     dp.stream = stream;
     int n = 0;
     for (auto& f : vec) {
+      cudaEvent_t e0 = nullptr, e1 = nullptr;
+      if (m->timing) { e0 = m->get_event(); e1 = m->get_event(); cudaEventRecord(e0, (cudaStream_t)stream); }
       const int rc = f.callback(dp);
+      if (m->timing) { cudaEventRecord(e1, (cudaStream_t)stream); m->ev_rec.push_back({f.name, {e0, e1}}); }
       if (rc != LIGER_OK) return rc;
       ++n;
     }

@@ -539,6 +539,8 @@ def run_decode(args, env):
     W = DECODE
     H = W["heads"] * W["head_dim"]
     B, L, cap = W["batch"], W["kv_len"], W["kv_capacity"]
+    if args.kv_len >= 0:   # 0: every token attends to itself only, the work the reference arm does (it has no cache)
+        L = min(args.kv_len, cap - 1)
     cfg = liger.default_config(max_batch_size=B, max_seq_len=8, head_num=W["heads"], size_per_head=W["head_dim"],
                                layer_num=args.layers, graph=1, act=1, ffn_inner=W["ffn_inner"], causal=1, seed=0,
                                workspace_slots=2, schedule_deep=1, kv_capacity=cap)
@@ -575,12 +577,25 @@ def run_decode(args, env):
         sampler.start()
     ms_total, launches, p50_ms = env.timed(step_device, args.steps)
     clocks = sampler.stop() if rank == 0 else None
+    # in-situ per-kernel durations (events between the kernels of the step), in a pass of its own
+    lib.liger_model_set_kernel_timing(model, 1)
+    env.barrier()
+    ksteps = min(args.steps, 10)
+    for _ in range(ksteps):
+        step_device()
+    kms = (C.c_double * 9)()
+    kcnt = (C.c_longlong * 9)()
+    liger.check(lib.liger_model_kernel_times(model, C.byref(kms), C.byref(kcnt)))
+    lib.liger_model_set_kernel_timing(model, 0)
+    env.barrier()
     for _ in range(2):
         step_host()
     ms_e2e, _, p50_e2e = env.timed(step_host, args.steps)
     env.check_device_status()
     parity = {"checked": False, "why": "fixture rows are for the 4-layer stack" if args.layers != W["layers"] else "fixture missing"}
-    if args.layers == W["layers"] and os.path.exists(GOLDEN_ROWS):
+    if L != W["kv_len"]:
+        parity["why"] = "fixture rows are for kv_len %d" % W["kv_len"]
+    elif args.layers == W["layers"] and os.path.exists(GOLDEN_ROWS):
         g = np.load(GOLDEN_ROWS)
         assert int(g["decode_kv_len"]) == L and int(g["decode_kv_capacity"]) == cap
         want = g["decode"].astype(np.float32)
@@ -593,11 +608,22 @@ def run_decode(args, env):
         step_bytes = args.layers * (weight_bytes + kv_bytes)
         step_ms = ms_total / args.steps
         achieved = step_bytes / (step_ms * 1e-3) / 1e9
+        Hl, Fl = H / world, F / world
+        kbytes = {0: 2 * H * 3 * Hl, 1: kv_bytes, 2: 2 * Hl * H, 4: 2 * H * 2 * Fl, 5: 2 * Fl * H}   # bytes each kernel must stream
+        names = {0: "qkv_gemm", 1: "attention", 2: "out_proj_gemm", 3: "allreduce_ln_1", 4: "ffn_up_gemm", 5: "ffn_down_gemm",
+                 6: "allreduce_ln_2", 7: "first_layernorm", 8: "copy_out"}
+        per_kernel = {}
+        for k in range(9):
+            if kcnt[k]:
+                avg_ms = kms[k] / kcnt[k]
+                per_kernel[names[k]] = {"avg_us": round(avg_ms * 1e3, 1), "launches_per_step": kcnt[k] // ksteps,
+                                        "gbs": round(kbytes[k] / avg_ms / 1e6, 1) if k in kbytes else None}
         line = {
             "metric": "tokens/s", "value": B * args.steps / (ms_total / 1e3), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_ms, "p50_latency_ms": p50_ms,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp16 (fp32 accumulate)", "data": "synthetic",
-            "config": {"workload": W["name"], "layers": args.layers, "hidden": H, "heads": W["heads"], "head_dim": W["head_dim"],
+            "config": {"workload": W["name"].replace("kv%d" % W["kv_len"], "kv%d" % L), "layers": args.layers, "hidden": H,
+                       "heads": W["heads"], "head_dim": W["head_dim"],
                        "ffn_inner": F, "activation": "geglu", "batch": B, "kv_len": L, "kv_capacity": cap, "tokens_per_step": B,
                        "parallelism": f"tp{world}",
                        "l2": f"inputs larger than L2: each step streams {step_bytes / 1e9:.2f} GB of weights and KV cache per rank"},
@@ -606,6 +632,7 @@ def run_decode(args, env):
                     "api": "liger_model_decode between a pinned-host upload of the token states and a download of the result"},
             "gpu_launches": launches,
             "parity": parity,
+            "kernels": per_kernel,
             "roofline": {"bound": "hbm", "kernel": "whole decode step (weight-streaming GEMMs + split-KV attention)",
                          "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                          "peak_source": peaks["source"] + ": STREAM-style copy", "traffic": None,
@@ -686,6 +713,8 @@ def main():
                     help="1: micro-requests on one compute stream + copy-engine all-gathers (default); 0: one stream per "
                          "micro-request; 2: whole batch, all-gather beside the GEMM that consumes it")
     ap.add_argument("--sweep-max-mb", type=int, default=512, help=argparse.SUPPRESS)
+    ap.add_argument("--kv-len", type=int, default=-1,
+                    help="decode: cached positions per sequence (default: the configuration's 2048); 0 = the reference arm's work")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

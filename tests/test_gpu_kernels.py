@@ -166,14 +166,20 @@ def test_gemm_residual(gpu, liger, oracle):
     assert_close(to_np(out), want, rel=1e-2, what="gemm+residual")
 
 
+SMALLM_KERNELS = {"auto": "1", "cluster": "2", "stream_k": "3"}   # values of LIGER_GEMM_SMALLM (read at every launch)
+
+
+@pytest.mark.parametrize("kernel", list(SMALLM_KERNELS))
 @pytest.mark.parametrize("epi", ["store", "gelu", "residual", "geglu", "qkv", "qkv_cache"])
 @pytest.mark.parametrize("m,k", [(32, 1024), (4, 136), (1, 4096), (17, 520)])
-def test_gemm_few_rows_weight_streaming_kernel(gpu, liger, oracle, epi, m, k):
-    """M <= 32 (a decode step) runs on the weight-streaming kernel: operand roles swapped (128 features x 32
-    tokens per accumulator), K split over a thread-block cluster and summed through distributed shared memory.
-    Every epilogue kind against the oracle, with K that is not a multiple of the 64-deep k-block, N that is not
-    a multiple of the 128-feature tile, and M below the 32-token tile."""
+def test_gemm_few_rows_weight_streaming_kernel(gpu, liger, oracle, monkeypatch, epi, m, k, kernel):
+    """M <= 32 (a decode step) runs on the weight-streaming kernels: operand roles swapped (128 features x 32
+    tokens per accumulator), K split either over a thread-block cluster (summed through distributed shared
+    memory) or evenly over all CTAs (partial tiles handed over through L2, summed by the last arrival).
+    Every epilogue kind against the oracle on either kernel, with K that is not a multiple of the 64-deep
+    k-block, N that is not a multiple of the 128-feature tile, and M below the 32-token tile."""
     import torch
+    monkeypatch.setenv("LIGER_GEMM_SMALLM", SMALLM_KERNELS[kernel])
     code = {"store": 0, "gelu": liger.capi.EPI_GELU, "residual": liger.capi.EPI_RESIDUAL, "geglu": liger.capi.EPI_GEGLU,
             "qkv": liger.capi.EPI_QKV_SPLIT, "qkv_cache": liger.capi.EPI_QKV_SPLIT}[epi]
     a = dev_fill(liger, m, k, 0, 400)
@@ -255,6 +261,32 @@ def test_gemm_few_rows_at_decode_shapes(gpu, liger):
         for r, c in zip(rows + [0, 31], cols):
             want = (a[r].double() * wt[c].double()).sum().item()
             assert abs(y[r, c].item() - want) <= 2e-3 * max(1.0, abs(want)), (n, k, r, c)
+
+
+def test_gemm_few_rows_stream_k_partitions(gpu, liger, monkeypatch):
+    """The stream-K kernel where a CTA's range of k-blocks crosses tile boundaries: a partial head, whole tiles in
+    the middle, a partial tail (38400 x 2560: 300 tiles x 40 k-blocks over 148 CTAs), and the two GLM-130B shapes
+    with few tiles and a long K.  Against the cluster kernel (same fp32 sums in another order: one rounding apart)
+    and against fp64 dot products of sampled entries; twice in a row, since the arrival counters alternate."""
+    import torch
+    for (n, k) in [(38400, 2560), (12288, 12288), (4608, 12288)]:
+        a = dev_fill(liger, 32, k, 0, 420, std=0.5)
+        wt = dev_fill(liger, k, n, 0, 421, std=0.02, mode=1)
+        monkeypatch.setenv("LIGER_GEMM_SMALLM", SMALLM_KERNELS["cluster"])
+        y_cluster = gemm(liger, a, wt)
+        monkeypatch.setenv("LIGER_GEMM_SMALLM", SMALLM_KERNELS["stream_k"])
+        y1 = gemm(liger, a, wt)
+        y2 = gemm(liger, a, wt)
+        check_status(liger)
+        assert torch.equal(y1, y2)                     # deterministic summation order
+        diff = (y1.float() - y_cluster.float()).abs()
+        assert bool((diff <= 2e-3 * y_cluster.float().abs().clamp(min=1.0)).all()), (n, k, diff.max().item())
+        g = torch.Generator().manual_seed(2)
+        rows = torch.randint(0, 32, (32,), generator=g).tolist()
+        cols = torch.randint(0, n, (32,), generator=g).tolist()
+        for r, c in zip(rows, cols):
+            want = (a[r].double() * wt[c].double()).sum().item()
+            assert abs(y1[r, c].item() - want) <= 2e-3 * max(1.0, abs(want)), (n, k, r, c)
 
 
 def test_gemm_linearity_at_full_size(gpu, liger):
