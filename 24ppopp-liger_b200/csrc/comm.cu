@@ -288,18 +288,26 @@ allreduce_fused_kernel(CommDev c, int channel, size_t partial_off, size_t recv_o
   }
 
   // ---- exit barrier: all of this rank's stores are visible before any rank moves on ----
-  __threadfence_system();
+  // One system-scope fence per CTA, by the thread that counts the CTA in, after the CTA barrier: fences are
+  // cumulative, so it covers the stores of all 256 threads (a fence per thread serialises in the memory pipeline).
+  // Without an exit barrier nothing is signalled and the end of the kernel publishes the (local) stores.
+  const bool exit_barrier = !(barrier_mode == 1 || barrier_mode == 3);
   __syncthreads();
   if (threadIdx.x == 0) {
+    if (exit_barrier) __threadfence_system();
     const unsigned int ticket = atomicAdd(done_counter, 1u);
-    if (ticket == gridDim.x - 1) { *done_counter = 0u; s_last = 1; }
+    if (ticket == gridDim.x - 1) {
+      *done_counter = 0u;
+      s_last = 1;
+      if (exit_barrier) __threadfence_system();  // the other CTAs' stores, seen through the counter, before the signal
+    }
   }
   __syncthreads();
-  if (s_last && (barrier_mode == 1 || barrier_mode == 3)) {
+  if (s_last && !exit_barrier) {
     if (threadIdx.x == 0) { stamps[2] = globaltimer_ns(); stamps[5] += stamps[2] - stamps[1]; stamps[7] += 1ull; }
   } else if (s_last) {
     const unsigned long long t_work = globaltimer_ns();
-    __threadfence_system();
+    if ((int)threadIdx.x < c.ws) __threadfence_system();
     barrier_signal(c, channel, epoch_out);
     barrier_wait(c, channel, epoch_out, &s_fail, st, 0x201u);
     if (threadIdx.x == 0) {
