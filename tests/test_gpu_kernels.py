@@ -289,6 +289,32 @@ def test_gemm_few_rows_stream_k_partitions(gpu, liger, monkeypatch):
             assert abs(y1[r, c].item() - want) <= 2e-3 * max(1.0, abs(want)), (n, k, r, c)
 
 
+def test_gemm_few_rows_stream_k_on_two_streams(gpu, liger, monkeypatch):
+    """Few-row GEMMs in flight on two streams at once: the stream-K kernel keeps its partial tiles and arrival
+    counters per stream, so concurrent launches must not disturb one another (same bits as one after the other)."""
+    import torch
+    monkeypatch.setenv("LIGER_GEMM_SMALLM", SMALLM_KERNELS["stream_k"])
+    n, k = 12288, 4096
+    a = [dev_fill(liger, 32, k, 0, 430 + i, std=0.5) for i in range(2)]
+    wt = [dev_fill(liger, k, n, 0, 432 + i, std=0.02, mode=1) for i in range(2)]
+    want = [gemm(liger, a[i], wt[i]) for i in range(2)]
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream() for _ in range(2)]
+    outs = [[torch.zeros_like(want[0]) for _ in range(6)] for _ in range(2)]
+    for rep in range(6):
+        for i in range(2):
+            args = liger.GemmArgs()
+            args.a, args.wt, args.c = a[i].data_ptr(), wt[i].data_ptr(), outs[i][rep].data_ptr()
+            args.m, args.n, args.k, args.lda, args.ldw, args.ldc = 32, n, k, k, k, n
+            args.n_begin, args.n_end, args.epilogue = 0, n, 0
+            liger.check(liger.lib().liger_gemm_fp16(C.byref(args), C.c_void_p(streams[i].cuda_stream)))
+    torch.cuda.synchronize()
+    check_status(liger)
+    for i in range(2):
+        for rep in range(6):
+            assert torch.equal(outs[i][rep], want[i]), (i, rep)
+
+
 def test_gemm_linearity_at_full_size(gpu, liger):
     """Size-independent property at the GLM-130B TP=8 QKV shape: (A1 + A2) W == A1 W + A2 W up to
     fp16 rounding, and a sampled set of entries against an fp64 dot product."""
