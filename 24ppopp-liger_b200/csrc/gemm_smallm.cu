@@ -80,52 +80,84 @@ __device__ __forceinline__ float4 sm_ld_cluster_f4(uint32_t cluster_addr) {
   return v;
 }
 
-// Finishes one 128-feature tile for the tokens t_first, t_first + t_step, ... < p.m: `sum8(t, fa, v)` adds the
-// fp32 sums of features fa .. fa + 7 of token t into v; bias / activation / layout follow, one 16-byte store per
-// (token, group of 8 output features).  Called by 128 threads (tid 0..127).
-template <typename Sum8>
-__device__ __forceinline__ void smallm_finish_tile(const GemmParams& p, int f0, int tid, int t_first, int t_step, Sum8 sum8) {
+// Finishing one 128-feature tile for the tokens t_first, t_first + t_step, ... < p.m: 128 threads (tid 0..127), each
+// with up to four items = (token, group of 8 output features), one 16-byte store per item.  The bias and residual
+// vectors of a thread's items do not depend on the accumulation, so they are fetched (smallm_prefetch) while the
+// weights are still streaming; smallm_finish_tile then only adds the sums: `sum8(t, fa, v)` adds the fp32 sums of
+// features fa .. fa + 7 of token t into v.  The four items are unrolled so that their loads overlap.
+constexpr int kSmItems = kSmTok * 16 / 128;  // items per thread at most (32 tokens x 16 groups over 128 threads)
+
+struct SmallmPrefetch {
+  uint4 bias[kSmItems], bias2[kSmItems], res[kSmItems];
+};
+
+struct SmallmItem {
+  int t, g, fa, n;
+  bool on;
+};
+
+__device__ __forceinline__ SmallmItem smallm_item(const GemmParams& p, int f0, int tid, int t_first, int t_step, int u) {
   const bool geglu = p.epilogue == LIGER_EPI_GEGLU;
   const int groups = geglu ? 8 : 16;  // 8-feature output groups per token
   const int my_tokens = (p.m - t_first + t_step - 1) / t_step;
-  for (int item = tid; item < my_tokens * groups; item += 128) {
-    const int t = t_first + t_step * (item / groups);
-    const int g = item % groups;
-    // features of this item inside the tile: plain kinds 8g..8g+7; GeGLU: gates 64b+8q.., values 64b+32+8q..
-    const int fa = geglu ? (g >> 2) * 64 + (g & 3) * 8 : g * 8;
-    const int n = f0 + fa;  // accumulator column (row of W^T)
-    if (n < p.n_begin || n >= p.n_end) continue;
-    float a[8] = {0, 0, 0, 0, 0, 0, 0, 0}, u[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    sum8(t, fa, a);
-    if (geglu) sum8(t, fa + 32, u);
+  const int item = tid + u * 128;
+  SmallmItem it;
+  it.t = t_first + t_step * (item / groups);
+  it.g = item % groups;
+  // features of this item inside the tile: plain kinds 8g..8g+7; GeGLU: gates 64b+8q.., values 64b+32+8q..
+  it.fa = geglu ? (it.g >> 2) * 64 + (it.g & 3) * 8 : it.g * 8;
+  it.n = f0 + it.fa;  // accumulator column (row of W^T)
+  it.on = item < my_tokens * groups && it.n >= p.n_begin && it.n < p.n_end;
+  return it;
+}
+
+__device__ __forceinline__ void smallm_prefetch(const GemmParams& p, int f0, int tid, int t_first, int t_step, SmallmPrefetch& pf) {
+#pragma unroll
+  for (int u = 0; u < kSmItems; ++u) {
+    const SmallmItem it = smallm_item(p, f0, tid, t_first, t_step, u);
+    pf.bias[u] = pf.bias2[u] = pf.res[u] = make_uint4(0, 0, 0, 0);
+    if (!it.on) continue;
     if (p.bias != nullptr) {
-      float b[8];
-      unpack8(__ldg(reinterpret_cast<const uint4*>(p.bias + n)), b);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) a[i] += b[i];
-      if (geglu) {
-        unpack8(__ldg(reinterpret_cast<const uint4*>(p.bias + n + 32)), b);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) u[i] += b[i];
-      }
+      pf.bias[u] = __ldg(reinterpret_cast<const uint4*>(p.bias + it.n));
+      if (p.epilogue == LIGER_EPI_GEGLU) pf.bias2[u] = __ldg(reinterpret_cast<const uint4*>(p.bias + it.n + 32));
     }
-    int out_col = n;
-    if (geglu) {
+    // plain load: the residual may be the very tensor this launch writes (each element by the thread that read it)
+    if (p.epilogue == LIGER_EPI_RESIDUAL) pf.res[u] = __ldcg(reinterpret_cast<const uint4*>(p.residual + (size_t)it.t * p.ldr + it.n));
+  }
+}
+
+template <typename Sum8>
+__device__ __forceinline__ void smallm_finish_tile(const GemmParams& p, int f0, int tid, int t_first, int t_step,
+                                                   const SmallmPrefetch& pf, Sum8 sum8) {
+  const bool geglu = p.epilogue == LIGER_EPI_GEGLU;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) a[i] = gelu_tanh(a[i]) * u[i];
-      out_col = (f0 >> 1) + (g >> 2) * 32 + (g & 3) * 8;
+  for (int u = 0; u < kSmItems; ++u) {
+    const SmallmItem it = smallm_item(p, f0, tid, t_first, t_step, u);
+    if (!it.on) continue;
+    float a[8] = {0, 0, 0, 0, 0, 0, 0, 0}, v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    sum8(it.t, it.fa, a);
+    if (geglu) sum8(it.t, it.fa + 32, v);
+    float b[8];
+    unpack8(pf.bias[u], b);  // zeros without a bias
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a[i] += b[i];
+    int out_col = it.n;
+    if (geglu) {
+      unpack8(pf.bias2[u], b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) a[i] = gelu_tanh(a[i]) * (v[i] + b[i]);
+      out_col = (f0 >> 1) + (it.g >> 2) * 32 + (it.g & 3) * 8;
     } else if (p.epilogue == LIGER_EPI_GELU) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) a[i] = gelu_tanh(a[i]);
     } else if (p.epilogue == LIGER_EPI_RESIDUAL) {
-      float b[8];
-      unpack8(__ldg(reinterpret_cast<const uint4*>(p.residual + (size_t)t * p.ldr + n)), b);
+      unpack8(pf.res[u], b);
 #pragma unroll
       for (int i = 0; i < 8; ++i) a[i] += b[i];
     }
     uint4 o;
     o.x = pack_half2(a[0], a[1]); o.y = pack_half2(a[2], a[3]); o.z = pack_half2(a[4], a[5]); o.w = pack_half2(a[6], a[7]);
-    *reinterpret_cast<uint4*>(epilogue_dst(p, t, out_col)) = o;
+    *reinterpret_cast<uint4*>(epilogue_dst(p, it.t, out_col)) = o;
   }
 }
 
@@ -175,6 +207,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  SmallmPrefetch pf;  // drain warps only
 
   if (warp == 0) {
     // ===== TMA producer: weights stream through once (evict first), the activations stay in L2 =====
@@ -213,6 +246,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
     // ===== drain: lane = feature, column = token -> partial[token][feature] (fp32) =====
     const int quad = warp & 3;
     const int f = quad * 32 + lane;
+    smallm_prefetch(p, f0, threadIdx.x - 64, split, splits, pf);  // bias / residual of this thread's items, meanwhile
     bool have = kb1 > kb0;
     if (have) have = mbar_wait_bounded(tmem_full, 0u, abort_flag);
     if (have) {
@@ -237,7 +271,7 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_cons
   if (warp >= 2 && *abort_flag == 0) {
     // ===== reduction over the cluster + epilogue: this CTA finishes tokens split, split + S, ... =====
     const uint32_t partial_local = smem_u32(partial);
-    smallm_finish_tile(p, f0, threadIdx.x - 64, split, splits, [&](int t, int fa, float (&v)[8]) {
+    smallm_finish_tile(p, f0, threadIdx.x - 64, split, splits, pf, [&](int t, int fa, float (&v)[8]) {
       for (int s = 0; s < splits; ++s) {  // fixed order: the result does not depend on timing
         const uint32_t base = sm_map_to_cta(partial_local, (uint32_t)s) + (uint32_t)((t * kSmFeat + fa) * 4);
         add8(v, sm_ld_cluster_f4(base), sm_ld_cluster_f4(base + 16));
@@ -386,6 +420,8 @@ gemm_smallm_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
       const int kb_hi = min(kblocks, kb_lo + (u_end - u));
       const int buf = seg & 1;
       const int f0 = tile * kSmFeat;
+      SmallmPrefetch pf;
+      smallm_prefetch(p, f0, tid, 0, 1, pf);  // bias / residual of this thread's items, while the segment streams
       if (!mbar_wait_bounded(&tmem_full[buf], (uint32_t)((seg >> 1) & 1), abort_flag)) *drain_abort = 1u;
       drain_bar_sync();
       if (*drain_abort) break;  // the same answer in all 128 threads: only written before the barrier
@@ -401,7 +437,7 @@ gemm_smallm_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
 #pragma unroll
         for (int t = 0; t < kSmTok; ++t) partial[t * kSmFeat + f] = __uint_as_float(r[t]);
         drain_bar_sync();
-        smallm_finish_tile(p, f0, tid, 0, 1, [&](int t, int fa, float (&v)[8]) {
+        smallm_finish_tile(p, f0, tid, 0, 1, pf, [&](int t, int fa, float (&v)[8]) {
           const float4* src = reinterpret_cast<const float4*>(partial + t * kSmFeat + fa);
           add8(v, src[0], src[1]);
         });
@@ -412,18 +448,18 @@ gemm_smallm_streamk_kernel(const __grid_constant__ CUtensorMap tmap_w, const __g
         float* dst = sk.ws + (size_t)(2 * c + (tile != first_tile ? 1 : 0)) * kSkSlotFloats;
 #pragma unroll
         for (int t = 0; t < kSmTok; ++t) __stcg(dst + t * kSmFeat + f, __uint_as_float(r[t]));
-        __threadfence();
         drain_bar_sync();
         const int c_first = (tile * kblocks) / sk.per;
         const int c_last = ((tile + 1) * kblocks - 1) / sk.per;
         if (tid == 0) {
+          __threadfence();  // one fence after the barrier covers all 128 threads' stores (fences are cumulative)
           const unsigned int old = atomicAdd(&sk.counters[tile], 1u);
+          __threadfence();  // the other CTAs' slots, seen through the counter, before this CTA reads them
           *last_flag = (old == (unsigned int)(c_last - c_first)) ? 1u : 0u;
         }
         drain_bar_sync();
         if (*last_flag) {
-          __threadfence();
-          smallm_finish_tile(p, f0, tid, 0, 1, [&](int t, int fa, float (&v)[8]) {
+          smallm_finish_tile(p, f0, tid, 0, 1, pf, [&](int t, int fa, float (&v)[8]) {
             for (int c0 = c_first; c0 <= c_last; c0 += 4) {  // fixed order: the result does not depend on timing
               float4 x[4][2];
 #pragma unroll
