@@ -98,6 +98,7 @@ SIGNATURES = {
     "liger_allgather_ce": (_I, [_P, _I, _SZ, _I, _I, _I, _I, _P]),
     "liger_allgather_push": (_I, [_P, _I, _I, _SZ, _I, _I, _P]),
     "liger_allreduce_ce": (_I, [_P, _I, _SZ, _SZ, _SZ, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
+    "liger_gemm_smallm_plan": (_I, [_I, _I, _I, C.POINTER(C.c_int)]),
     "liger_allreduce_fused": (_I, [_P, _I, _SZ, _SZ, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "liger_model_config_init": (None, [C.POINTER(ModelConfig)]),
     "liger_model_comm_bytes": (_SZ, [C.POINTER(ModelConfig), _I]),

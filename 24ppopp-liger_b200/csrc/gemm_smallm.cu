@@ -599,6 +599,49 @@ static int launch_streamk(const liger_gemm_args& a, const GemmParams& p, const D
   return check_launch("gemm_smallm_streamk_kernel");
 }
 
+// Which kernel a few-row GEMM over an [n, k] weight takes, and with what split.  A pure function of the whole
+// weight, the SM count and conc[s] = clusters of s CTAs that run at once, so that every slice [n_begin, n_end) of
+// a weight takes the same kernel, the same k-ranges and the same summation order.  Costs are in k-block times.
+struct SmallmPlan {
+  bool stream_k;      // false: cluster kernel with `splits` CTAs per tile
+  int splits;
+  int per;            // stream-K: k-blocks per CTA
+  bool partial;       // stream-K: some tile is shared between CTAs
+  long cluster_cost, stream_k_cost;
+};
+
+static SmallmPlan smallm_plan(int n, int k, int sm_count, const int* conc, int mode, int forced_splits) {
+  SmallmPlan pl = {};
+  const int kblocks = (k + BK - 1) / BK;
+  const int tiles_full = (n + kSmFeat - 1) / kSmFeat;
+  // Above about 0.9 x sm_count streaming CTAs HBM, not the SM, sets the pace: no schedule streams the weight in
+  // fewer k-block times than this floor.
+  const long hbm_floor = (long)tiles_full * kblocks * 11 / (10L * sm_count);
+  // Cluster kernel: waves x (k-blocks per CTA + a set-up / drain term).  Measured on B200 a CTA streams a 16 KB
+  // k-block in about 0.34 us and spends about 8 us outside its main loop; a cluster of s CTAs needs s free SMs in
+  // one GPC, so fewer clusters than sm_count / s run at once, and a second wave of clusters starts raggedly
+  // (x 1.4, fitted to the GLM-130B decode shapes).
+  pl.splits = 1;
+  pl.cluster_cost = -1;
+  for (int s = 1; s <= kSmMaxSplits && s <= kblocks; ++s) {
+    const long c = conc[s] > 0 ? conc[s] : 1;
+    const long waves = (tiles_full + c - 1) / c;
+    long cost = std::max(waves * ((kblocks + s - 1) / s), hbm_floor) + waves * 24;
+    if (waves > 1) cost += cost * 2 / 5;
+    if (pl.cluster_cost < 0 || cost < pl.cluster_cost) { pl.cluster_cost = cost; pl.splits = s; }
+  }
+  if (forced_splits > 0 && forced_splits <= kSmMaxSplits && forced_splits <= kblocks) pl.splits = forced_splits;
+  // Stream-K kernel: every SM streams `per` k-blocks; handing partial tiles over through L2 costs about 9 us more
+  // than a kernel that finishes whole tiles (measured at the same shapes).
+  const bool possible = tiles_full <= kSkMaxTiles && (long)tiles_full * kblocks < (1l << 24);
+  if (possible) {
+    pl.per = streamk_units_per_cta(tiles_full, kblocks, sm_count, &pl.partial);
+    pl.stream_k_cost = std::max((long)pl.per, hbm_floor) + (pl.partial ? 46 : 20);
+  }
+  pl.stream_k = possible && (mode == 3 || (mode != 2 && pl.stream_k_cost < pl.cluster_cost));
+  return pl;
+}
+
 // Returns LIGER_ERR_UNSUPPORTED (error text untouched) when the shape is not this kernel's.
 int launch_gemm_smallm(const liger_gemm_args& a, const GemmParams& p0, const DeviceInfo* dev, cudaStream_t stream) {
   const int mode = smallm_mode();
@@ -606,34 +649,13 @@ int launch_gemm_smallm(const liger_gemm_args& a, const GemmParams& p0, const Dev
   GemmParams p = p0;
   p.kblocks = (a.k + BK - 1) / BK;
   const int tiles = (a.n_end - a.n_begin + kSmFeat - 1) / kSmFeat;
-  const int tiles_full = (a.n + kSmFeat - 1) / kSmFeat;
-  // Cluster kernel: cost of a split count in k-block times, waves x (k-blocks per CTA + a set-up / drain term).
-  // Measured on B200 a CTA streams a 16 KB k-block in about 0.34 us and spends about 8 us outside its main loop; a
-  // cluster of s CTAs needs s free SMs in one GPC, so fewer clusters than sm_count / s run at once, and a second
-  // wave of clusters starts raggedly (x 1.4, fitted to the GLM-130B decode shapes).  The split count is chosen from
-  // the whole weight (a.n), not from the slice being computed: slices give the bits of the whole launch.
-  // Above about 0.9 x sm_count streaming CTAs HBM, not the SM, sets the pace: no schedule streams the weight in fewer
-  // k-block times than this floor.
-  const long hbm_floor = (long)tiles_full * p.kblocks * 11 / (10L * dev->sm_count);
+  int conc[kSmMaxSplits + 1] = {0};
+  for (int s = 1; s <= kSmMaxSplits; ++s) conc[s] = smallm_max_clusters(dev->device, dev->sm_count, s);
   static int forced = -1;
   if (forced < 0) { const char* e = getenv("LIGER_GEMM_SMALLM_SPLITS"); forced = e ? atoi(e) : 0; }
-  int best = 1;
-  long best_cost = -1;
-  for (int s = 1; s <= kSmMaxSplits && s <= p.kblocks; ++s) {
-    const long conc = smallm_max_clusters(dev->device, dev->sm_count, s);
-    const long waves = (tiles_full + conc - 1) / conc;
-    long cost = std::max(waves * ((p.kblocks + s - 1) / s), hbm_floor) + waves * 24;
-    if (waves > 1) cost += cost * 2 / 5;
-    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = s; }
-  }
-  if (forced > 0 && forced <= kSmMaxSplits && forced <= p.kblocks) best = forced;
-  // Stream-K kernel: every SM streams `per` k-blocks; handing partial tiles over through L2 costs about 9 us more
-  // than a kernel that finishes whole tiles (measured at the same shapes).
-  const bool sk_possible = tiles_full <= kSkMaxTiles && (long)tiles_full * p.kblocks < (1l << 24);
-  bool sk_partial = false;
-  const long sk_per = sk_possible ? streamk_units_per_cta(tiles_full, p.kblocks, dev->sm_count, &sk_partial) : 0;
-  const long sk_cost = std::max(sk_per, hbm_floor) + (sk_partial ? 46 : 20);
-  const bool use_sk = sk_possible && (mode == 3 || (mode != 2 && sk_cost < best_cost));
+  const SmallmPlan plan = smallm_plan(a.n, a.k, dev->sm_count, conc, mode, forced);
+  const int best = plan.splits;
+  const bool use_sk = plan.stream_k;
   if (!use_sk && a.epilogue == LIGER_EPI_GEGLU && a.n_begin % 128) return LIGER_ERR_UNSUPPORTED;  // gate / value pairs per tile
   CUtensorMap tm_w, tm_x;
   int rc;
@@ -656,3 +678,18 @@ int launch_gemm_smallm(const liger_gemm_args& a, const GemmParams& p0, const Dev
 }
 
 }  // namespace liger
+
+extern "C" int liger_gemm_smallm_plan(int n, int k, int sm_count, int out[4]) {
+  using namespace liger;
+  if (n <= 0 || k <= 0 || sm_count <= 0 || !out) return set_error(LIGER_ERR_INVALID, "gemm_smallm_plan: bad argument");
+  // clusters that run at once by GPC geometry alone (8 GPCs); a launch asks the device as well
+  int conc[kSmMaxSplits + 1] = {0};
+  for (int s = 1; s <= kSmMaxSplits; ++s) conc[s] = s < 3 ? sm_count / s : 8 * ((sm_count / 8) / s);
+  const SmallmPlan pl = smallm_plan(n, k, sm_count, conc, 1, 0);
+  const int kblocks = (k + BK - 1) / BK, tiles = (n + kSmFeat - 1) / kSmFeat;
+  out[0] = pl.stream_k ? 3 : 2;
+  out[1] = pl.stream_k ? 1 : pl.splits;
+  out[2] = pl.stream_k ? pl.per : (kblocks + pl.splits - 1) / pl.splits;
+  out[3] = pl.stream_k ? (tiles * kblocks + pl.per - 1) / pl.per : tiles * pl.splits;
+  return LIGER_OK;
+}

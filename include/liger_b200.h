@@ -289,6 +289,15 @@ LIGER_API int liger_comm_channels(liger_comm* comm);
 LIGER_API int liger_comm_timing(liger_comm* comm, int channel, int reset, double out_us[4]);
 
 /*
+ * Which of the two few-row kernels (M <= 32) liger_gemm_fp16 takes for an [n, k] weight on a GPU with sm_count SMs,
+ * without launching anything (no GPU needed): out[0] = 2 cluster kernel / 3 stream-K kernel, out[1] = CTAs per
+ * cluster (K splits; 1 for stream-K), out[2] = 64-deep k-blocks each CTA streams, out[3] = CTAs of the launch.
+ * The choice depends on the whole weight only, never on the slice [n_begin, n_end) being computed.  The reference
+ * has no counterpart (one cuBLAS heuristic call per GEMM, src/layer/func_wrapper.h:20-27).
+ */
+LIGER_API int liger_gemm_smallm_plan(int n, int k, int sm_count, int out[4]);
+
+/*
  * All-reduce (sum over ranks) of the row-parallel partials, fused with what follows it in the layer.
  * Replaces Allreduce (src/layer/func_wrapper.h:40-43, bound at src/layer/linear.h:55-60) together
  * with the residual / LayerNorm kernel after it (Layer_Norm, src/layer/func_wrapper.h:110-114, or

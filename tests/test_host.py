@@ -140,3 +140,60 @@ def test_cost_model_interpolates_between_profiled_shapes(liger, tmp_path):
     assert predict(4, 16, 192) == pytest.approx((0.2 + 1.92) * 2.0, rel=1e-6)
     assert predict(5, 8, 256) == 0.0                                                    # never profiled
     assert lib.liger_profile_predict(None, 16, 1024, 4, 8, 256, None) == -1
+
+
+def test_few_row_gemm_plan_covers_every_k_block_once(liger):
+    """The host-side choice between the two few-row GEMM kernels (liger_gemm_smallm_plan; no GPU involved).
+    For the stream-K kernel the plan is `per` k-blocks per CTA over the tile-major line of (tile, k-block) pairs:
+    replaying the kernel's own arithmetic, every k-block of every tile is covered exactly once, a CTA hands over
+    at most two partial tiles (its first and its last) into distinct slots, and the contributors the last arrival
+    sums for a tile are exactly the CTAs that touched it.  For the cluster kernel the splits cover K and the
+    grid is tiles x splits.  And at the shapes of a GLM-130B decode step the long-K / few-tile weights
+    (out-projection and FFN-down at TP = 1) go to stream-K, the TP = 8 QKV weight to a single wave of clusters."""
+    lib = liger.lib()
+
+    def plan(n, k, sm):
+        out = (C.c_int * 4)()
+        assert lib.liger_gemm_smallm_plan(n, k, sm, out) == 0
+        return list(out)
+
+    import random
+    rnd = random.Random(7)
+    cases = [(12288, 12288, 148), (12288, 32768, 148), (36864, 12288, 148), (65536, 12288, 148), (4608, 12288, 148),
+             (12288, 1536, 148), (1096, 1024, 148), (8, 8, 148), (38400, 2560, 148)]
+    cases += [(8 * rnd.randint(1, 6000), 8 * rnd.randint(1, 3000), rnd.choice([148, 132, 16])) for _ in range(300)]
+    seen = set()
+    for (n, k, sm) in cases:
+        kernel, splits, per, ctas = plan(n, k, sm)
+        tiles, kblocks = -(-n // 128), -(-k // 64)
+        seen.add(kernel)
+        if kernel == 2:
+            assert 1 <= splits <= 8 and splits <= kblocks and ctas == tiles * splits and per * splits >= kblocks
+            continue
+        assert kernel == 3 and splits == 1 and ctas <= sm and ctas == -(-tiles * kblocks // per)
+        covered, slots, touched = {}, set(), {}
+        for c in range(ctas):
+            u, end, parts = c * per, min((c + 1) * per, tiles * kblocks), 0
+            assert u < end
+            while u < end:
+                t = u // kblocks
+                lo = u - t * kblocks
+                hi = min(kblocks, lo + end - u)
+                covered.setdefault(t, []).append((lo, hi))
+                if not (lo == 0 and hi == kblocks):
+                    slot = 2 * c + (1 if t != (c * per) // kblocks else 0)
+                    assert slot not in slots
+                    slots.add(slot)
+                    touched.setdefault(t, []).append(c)
+                    parts += 1
+                u += hi - lo
+            assert parts <= 2
+        for t in range(tiles):
+            segs = sorted(covered[t])
+            assert segs[0][0] == 0 and segs[-1][1] == kblocks and all(a[1] == b[0] for a, b in zip(segs, segs[1:]))
+            first, last = (t * kblocks) // per, ((t + 1) * kblocks - 1) // per
+            assert touched.get(t, [first]) == list(range(first, last + 1)) or (t not in touched and first == last)
+    assert seen == {2, 3}
+    assert plan(12288, 12288, 148)[0] == 3 and plan(12288, 32768, 148)[0] == 3     # long K, 96 tiles
+    assert plan(4608, 12288, 148)[:2] == [2, 4] or plan(4608, 12288, 148)[:2] == [2, 3]   # one wave of clusters
+    assert lib.liger_gemm_smallm_plan(0, 64, 148, (C.c_int * 4)()) < 0
