@@ -486,6 +486,35 @@ def test_attention_prefill(gpu, liger, oracle, B, h, S, D, mode):
     check_status(liger)
 
 
+def test_attention_decode_cache_larger_than_l2(gpu, liger, oracle):
+    """The benchmark's per-layer decode attention at a quarter of its batch: 8 sequences x 96 heads x 2048 cached
+    positions x 128 (805 MB of K and V, read once from HBM).  Sixteen sampled (sequence, head) pairs against the
+    oracle; the result does not depend on the order in which the 256-key chunks finish (two runs, same bits)."""
+    import torch
+    B, h, L, D = 8, 96, 2048, 128
+    Lmax = L + 64
+    q = dev_fill(liger, B * h, D, 0, 410).reshape(B, h, D)
+    kc = dev_fill(liger, B * h * Lmax, D, 0, oracle.KCACHE).reshape(B, h, Lmax, D)
+    vc = dev_fill(liger, B * h * Lmax, D, 0, oracle.VCACHE).reshape(B, h, Lmax, D)
+    nbytes = liger.lib().liger_attention_decode_scratch_bytes(B, h, D, L)
+    scratch = torch.empty(nbytes // 4, dtype=torch.float32, device="cuda")
+    scale = 1.0 / np.sqrt(D)
+    outs = []
+    for _ in range(2):
+        out = torch.zeros((B, h * D), dtype=torch.float16, device="cuda")
+        liger.check(liger.lib().liger_attention_decode(ptr(q), ptr(kc), ptr(vc), ptr(out), ptr(scratch), B, h, L, Lmax, D,
+                                                       h * D, scale, stream_ptr()))
+        outs.append(out)
+    check_status(liger)
+    assert torch.equal(outs[0], outs[1])
+    g = torch.Generator().manual_seed(3)
+    got = to_np(outs[0]).reshape(B, h, D)
+    for b, hd in zip(torch.randint(0, B, (16,), generator=g).tolist(), torch.randint(0, h, (16,), generator=g).tolist()):
+        want = oracle.attention(to_np(q[b:b + 1, hd:hd + 1])[:, :, None, :], to_np(kc[b:b + 1, hd:hd + 1, :L]),
+                                to_np(vc[b:b + 1, hd:hd + 1, :L]), causal=True, scale=scale)
+        assert_close(got[b, hd], want.reshape(D), rel=1e-2, what=f"decode attention ({b}, {hd})")
+
+
 @pytest.mark.parametrize("B,h,L,D", [(2, 3, 300, 128), (4, 2, 2048, 128), (1, 2, 17, 64), (3, 1, 256, 64)])
 def test_attention_decode(gpu, liger, oracle, B, h, L, D):
     import torch
