@@ -153,6 +153,11 @@ REF_HARNESS = os.path.join(ROOT, "oracle", "_ref", "liger_ref_harness")
 # DRAM bytes per GEMM launch at N=1 (read + write, average of the QKV / out-proj / FFN-up / FFN-down launches of
 # one layer), from the one-pass ncu capture summarised under profiles/.
 GEMM_DRAM_BYTES_PER_LAUNCH_TP1 = 4.44e9
+# Decode: DRAM bytes (read + write) per algorithmic byte of the two kernels that make up a step, from ncu captures
+# of smaller cases (a full step holds 27 GB): 304.1 + 4.3 MB for the 303.6 MB of the 32 x 12288 x 12288 few-row
+# GEMM, 805.6 + 6.3 MB for the 805.3 MB of decode attention over 8 of the 32 sequences.
+GEMM_SMALLM_TRAFFIC_RATIO = (304.1 + 4.3) / 303.6
+ATTENTION_DECODE_TRAFFIC_RATIO = (805.6 + 6.3) / 805.3
 
 
 # ---- the reference arm ------------------------------------------------------------------------------------
@@ -606,6 +611,7 @@ def run_decode(args, env):
         weight_bytes = (4 * H * H + 3 * H * F) * 2 / world
         kv_bytes = 2 * B * (W["heads"] / world) * (L + 1) * W["head_dim"] * 2
         step_bytes = args.layers * (weight_bytes + kv_bytes)
+        decode_traffic = args.layers * (weight_bytes * GEMM_SMALLM_TRAFFIC_RATIO + kv_bytes * ATTENTION_DECODE_TRAFFIC_RATIO)
         step_ms = ms_total / args.steps
         achieved = step_bytes / (step_ms * 1e-3) / 1e9
         Hl, Fl = H / world, F / world
@@ -635,7 +641,11 @@ def run_decode(args, env):
             "kernels": per_kernel,
             "roofline": {"bound": "hbm", "kernel": "whole decode step (weight-streaming GEMMs + split-KV attention)",
                          "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                         "peak_source": peaks["source"] + ": STREAM-style copy", "traffic": None,
+                         "peak_source": peaks["source"] + ": STREAM-style copy",
+                         "traffic": decode_traffic if world == 1 and L == W["kv_len"] else None,
+                         "traffic_source": "ncu dram read+write of the two kernels on smaller cases, scaled by bytes streamed: "
+                                           "few-row GEMM x %.4f (32 x 12288 x 12288), decode attention x %.4f (8 of 32 sequences); "
+                                           "see profiles/" % (GEMM_SMALLM_TRAFFIC_RATIO, ATTENTION_DECODE_TRAFFIC_RATIO),
                          "bytes_per_step_per_rank": step_bytes},
             "clocks": clocks,
         }
